@@ -1,0 +1,80 @@
+// Shared helpers of the sm_100a kernels: element types, reductions with a fixed order,
+// the error string that the C entry points leave for the Python side.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define FRB_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+// Element type codes used by every entry point.
+enum FrbDtype { FRB_F32 = 0, FRB_BF16 = 1 };
+
+// Tokens per cache page; must equal PAGE_TOKENS of the Python cache.
+#define FRB_PAGE 64
+
+void frb_set_error(const char* fmt, ...);
+
+#define FRB_CHECK_ARG(cond, ...)            \
+    do {                                    \
+        if (!(cond)) {                      \
+            frb_set_error(__VA_ARGS__);     \
+            return -1;                      \
+        }                                   \
+    } while (0)
+
+#define FRB_RETURN_LAUNCH(name)                                                   \
+    do {                                                                          \
+        cudaError_t frb_e_ = cudaGetLastError();                                  \
+        if (frb_e_ != cudaSuccess) {                                              \
+            frb_set_error("%s: launch failed: %s", name, cudaGetErrorString(frb_e_)); \
+            return (int)frb_e_;                                                   \
+        }                                                                         \
+        return 0;                                                                 \
+    } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of BLOCK threads; every thread gets the result.  The order of additions depends on
+// BLOCK only, so a row's sum is the same whatever else the launch holds.  `scratch` holds 32 floats.
+template <int BLOCK>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();                      // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < BLOCK / 32; ++w) total += scratch[w];
+    return total;
+}
+
+// Calls `body` with a value of the element type that `code` names.
+#define FRB_DISPATCH_DTYPE(code, T, ...)                          \
+    do {                                                          \
+        if ((code) == FRB_F32) { typedef float T; __VA_ARGS__; }  \
+        else { typedef bf16 T; __VA_ARGS__; }                     \
+    } while (0)

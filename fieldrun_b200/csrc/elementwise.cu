@@ -1,0 +1,247 @@
+// Row-wise kernels: embedding rows, RMSNorm fused with the residual add that precedes it,
+// and the step between the QKV product and attention (full-width Q/K RMSNorm, rotary on the
+// first rotary_dim dims of each head, write of K and V into the paged cache).
+//
+// Formulas follow the reference's CPU code: norm x*rsqrt(mean(x^2)+eps)*w (src/minimax.rs:56-66),
+// rotate-half pairs (j, j+half) by pos*inv[j] (src/minimax.rs:69-84, partial form
+// src/qwen35moe.rs:121-138), K cached after norm and rotary, V as projected (src/minimax.rs:262-268).
+// All statistics and the residual sum are float32.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[1024] = "";
+
+void frb_set_error(const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, args);
+    va_end(args);
+}
+
+FRB_API const char* frb_last_error() { return g_error; }
+
+FRB_API int frb_abi_version() { return 3; }
+
+// ----------------------------------------------------------------------------- embedding rows
+
+template <typename WT>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const WT* __restrict__ table, float* __restrict__ out,
+                                  int width, int vocab) {
+    const int t = blockIdx.x;
+    int token = tokens[t];
+    if (token < 0 || token >= vocab) token = 0;      // ids are checked on the host before any launch
+    const WT* row = table + (size_t)token * width;
+    float* dst = out + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32<WT>(row[i]);
+}
+
+// out[t, :] = table[tokens[t], :] widened to float32 (no multiplier, src/minimax.rs:132).
+FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype, float* out, int num_tokens,
+                           int width, int vocab, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_DISPATCH_DTYPE(table_dtype, WT, {
+        embed_rows_kernel<WT><<<num_tokens, 256, 0, stream>>>(tokens, (const WT*)table, out, width, vocab);
+    });
+    FRB_RETURN_LAUNCH("embed_rows");
+}
+
+// ----------------------------------------------------------------------------- RMSNorm (+ residual add)
+
+#define NORM_BLOCK 256
+
+// One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]); if write_back the
+// sum is stored to x[src] (the residual stream).  out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and,
+// when out32 is given, in float32 as well.
+template <typename OutT, typename WT>
+__global__ void __launch_bounds__(NORM_BLOCK)
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const int* __restrict__ rows,
+               const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
+               int write_back) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* xr = x + (size_t)src * width;
+    const float* dr = delta ? delta + (size_t)src * width : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
+        float v = xr[i];
+        if (dr) v += dr[i];
+        row[i] = v;
+        ss += v * v;
+        if (write_back) xr[i] = v;
+    }
+    ss = block_sum<NORM_BLOCK>(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
+        const float y = row[i] * rinv * to_f32<WT>(weight[i]);
+        out[(size_t)r * width + i] = from_f32<OutT>(y);
+        if (out32) out32[(size_t)r * width + i] = y;
+    }
+}
+
+FRB_API int frb_rmsnorm(float* x, const float* delta, const int* rows, const void* weight, int weight_dtype,
+                        float eps, int num_rows, int width, void* out, int out_dtype, float* out32,
+                        int write_back, cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    FRB_CHECK_ARG(smem <= 200 * 1024, "rmsnorm: width %d needs %zu bytes of shared memory, more than 200 KB", width, smem);
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
+        auto kernel = rmsnorm_kernel<OutT, WT>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<num_rows, NORM_BLOCK, smem, stream>>>(x, delta, rows, (const WT*)weight, eps, width, (OutT*)out,
+                                                       out32, write_back);
+    }));
+    FRB_RETURN_LAUNCH("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------- Q/K norm + rotary + cache write
+
+struct QkvParams {
+    const void* qkv;          // [T, (nh + 2 nkv) * hd], InT
+    const void* q_weight;     // [nh*hd] or null: no norm
+    const void* k_weight;     // [nkv*hd] or null
+    const float* cos_table;   // [positions, rotary_dim/2]
+    const float* sin_table;
+    const int* tok_pos;       // [T] absolute position
+    const int* tok_slot;      // [T] cache slot
+    const int* page_table;    // [slots, max_pages]
+    void* q_out;              // [T, nh, hd] OutT
+    void* k_pages;            // [pages, nkv, PAGE, hd] OutT
+    void* v_pages;
+    float eps;
+    int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
+};
+
+template <typename WT>
+__device__ __forceinline__ float normed(const float* raw, const WT* w, float rinv, int i) {
+    return w ? raw[i] * rinv * to_f32<WT>(w[i]) : raw[i];
+}
+
+// One block per token.  The raw Q and K rows sit in shared memory; each thread produces output elements
+// from the raw values of its own element and of its rotation partner.
+template <typename InT, typename OutT, typename WT>
+__global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
+    extern __shared__ float raw[];           // [(nh + nkv) * hd] : Q row then K row
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int hd = p.head_dim;
+    const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
+    const InT* src = (const InT*)p.qkv + (size_t)t * (q_width + 2 * k_width);
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < q_width + k_width; i += NORM_BLOCK) {
+        const float v = to_f32<InT>(src[i]);
+        raw[i] = v;
+        if (i < q_width) ssq += v * v; else ssk += v * v;
+    }
+    const WT* qw = (const WT*)p.q_weight;
+    const WT* kw = (const WT*)p.k_weight;
+    float rinv_q = 1.f, rinv_k = 1.f;
+    if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
+    if (kw) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
+    __syncthreads();
+
+    const int pos = p.tok_pos[t];
+    const int slot = p.tok_slot[t];
+    const int half = p.rotary_dim / 2;
+    const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
+    const float* cs = p.cos_table + (size_t)table_row * half;
+    const float* sn = p.sin_table + (size_t)table_row * half;
+    const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
+    const int in_page = pos % FRB_PAGE;
+
+    for (int i = threadIdx.x; i < q_width + k_width; i += NORM_BLOCK) {
+        const bool is_q = i < q_width;
+        const float* base = is_q ? raw : raw + q_width;
+        const WT* w = is_q ? qw : kw;
+        const float rinv = is_q ? rinv_q : rinv_k;
+        const int local = is_q ? i : i - q_width;
+        const int head = local / hd, dim = local % hd;
+        float value = normed<WT>(base, w, rinv, local);
+        if (dim < p.rotary_dim) {
+            int j, partner;
+            bool first;
+            if (p.interleaved) { j = dim >> 1; first = (dim & 1) == 0; partner = first ? local + 1 : local - 1; }
+            else { first = dim < half; j = first ? dim : dim - half; partner = first ? local + half : local - half; }
+            const float other = normed<WT>(base, w, rinv, partner);
+            const float c = cs[j], s = sn[j];
+            // a' = a c - b s ; b' = b c + a s   (src/minimax.rs:78-81)
+            value = first ? value * c - other * s : value * c + other * s;
+        }
+        if (is_q) {
+            ((OutT*)p.q_out)[(size_t)t * q_width + local] = from_f32<OutT>(value);
+        } else if (page >= 0) {
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * FRB_PAGE + in_page) * hd + dim;
+            ((OutT*)p.k_pages)[at] = from_f32<OutT>(value);
+        }
+    }
+    if (page >= 0) {
+        const InT* vsrc = src + q_width + k_width;
+        for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
+            const int head = i / hd, dim = i % hd;
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * FRB_PAGE + in_page) * hd + dim;
+            ((OutT*)p.v_pages)[at] = from_f32<OutT>(to_f32<InT>(vsrc[i]));
+        }
+    }
+}
+
+FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight, const void* k_weight, int weight_dtype,
+                            float eps, const float* cos_table, const float* sin_table, int table_positions,
+                            const int* tok_pos, const int* tok_slot, const int* page_table, int max_pages,
+                            void* q_out, void* k_pages, void* v_pages, int out_dtype, int num_tokens, int num_heads,
+                            int num_kv_heads, int head_dim, int rotary_dim, int interleaved, int write_cache,
+                            cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_CHECK_ARG(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "qkv_prepare: rotary_dim %d must be even and <= head_dim %d",
+                  rotary_dim, head_dim);
+    FRB_CHECK_ARG(rotary_dim == 0 || (cos_table && sin_table && table_positions > 0), "qkv_prepare: rotary tables are missing");
+    QkvParams p;
+    p.qkv = qkv; p.q_weight = q_weight; p.k_weight = k_weight; p.cos_table = cos_table; p.sin_table = sin_table;
+    p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.page_table = page_table; p.q_out = q_out; p.k_pages = k_pages;
+    p.v_pages = v_pages; p.eps = eps; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
+    p.rotary_dim = rotary_dim; p.interleaved = interleaved; p.max_pages = max_pages; p.write_cache = write_cache;
+    p.table_positions = table_positions;
+    const size_t smem = (size_t)(num_heads + num_kv_heads) * head_dim * sizeof(float);
+    FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + kv heads) * head_dim = %d needs more than 200 KB of shared memory",
+                  (num_heads + num_kv_heads) * head_dim);
+    FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
+        auto kernel = qkv_prepare_kernel<InT, OutT, WT>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<num_tokens, NORM_BLOCK, smem, stream>>>(p);
+    })));
+    FRB_RETURN_LAUNCH("qkv_prepare");
+}
+
+// ----------------------------------------------------------------------------- small helpers
+
+// x[i] += delta[i]  (float32 residual sum when no norm follows)
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += delta[i];
+}
+
+FRB_API int frb_add_rows(float* x, const float* delta, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    add_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, delta, (size_t)n);
+    FRB_RETURN_LAUNCH("add_rows");
+}
+
+// out[t, i] = silu(both[t, i]) * both[t, width + i], silu(x) = x / (1 + exp(-x))  (src/minimax.rs:31,119)
+template <typename OutT>
+__global__ void gated_unit_kernel(const float* __restrict__ both, OutT* __restrict__ out, int width, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / width, c = i - t * width;
+    const float g = both[t * 2 * width + c], u = both[t * 2 * width + width + c];
+    out[i] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
+}
+
+FRB_API int frb_gated_unit(const float* both, void* out, int out_dtype, int rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    if (total == 0) return 0;
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        gated_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(both, (OutT*)out, width, total);
+    });
+    FRB_RETURN_LAUNCH("gated_unit");
+}

@@ -1,0 +1,227 @@
+"""Python face of the compiled kernels: loads the shared library through ctypes and
+launches each entry point on torch's current CUDA stream with raw device pointers.
+
+There is no other implementation behind these functions.  If the library cannot
+be built or loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_LIB: ctypes.CDLL | None = None
+_LIB_PATH: str | None = None
+
+_P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+# entry point -> argument types ('p' pointer, 'i' int, 'f' float, 'l' long long); the stream is appended
+_SIGNATURES = {
+    "frb_embed_rows": "ppipiii",
+    "frb_rmsnorm": "ppppifiipipi",
+    "frb_qkv_prepare": "pippifppipppipppiiiiiiii",
+    "frb_add_rows": "ppl",
+    "frb_attention_generic": "pppipipppiiiifi",
+    "frb_router_topk": "ppiiiifpp",
+    "frb_expert_plan": "piiiippppppp",
+    "frb_expert_combine": "pppiiip",
+    "frb_expert_gemm_generic": "ppipppppipiiii",
+    "frb_sample_rows": "piippp",
+    "frb_gated_unit": "ppiii",
+}
+_CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The compiled kernels; built at the first call."""
+    global _LIB, _LIB_PATH
+    if _LIB is None:
+        path = _build.build()
+        lib = ctypes.CDLL(path)
+        lib.frb_last_error.restype = ctypes.c_char_p
+        lib.frb_last_error.argtypes = []
+        for name, spec in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = [_CTYPE[c] for c in spec] + [_P]
+        _LIB, _LIB_PATH = lib, path
+    return _LIB
+
+
+def library_file() -> str:
+    library()
+    assert _LIB_PATH is not None
+    return _LIB_PATH
+
+
+def register(name: str, spec: str) -> None:
+    """Declare one more entry point of the library (used by kernels that live in files of their own)."""
+    _SIGNATURES[name] = spec
+    if _LIB is not None:
+        fn = getattr(_LIB, name)
+        fn.restype = _I
+        fn.argtypes = [_CTYPE[c] for c in spec] + [_P]
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"the kernels take float32 and bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a CPU tensor was given to a CUDA kernel; fieldrun_b200 has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError("a kernel was given a tensor that is not contiguous")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _call(name: str, *args) -> None:
+    lib = library()
+    status = getattr(lib, name)(*args, _stream())
+    if status != 0:
+        raise KernelError(f"{name}: {lib.frb_last_error().decode(errors='replace')} (status {status})")
+
+
+def _want(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+    if t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, found {t.dtype}")
+
+
+# ------------------------------------------------------------------------------------------------
+
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[tokens[t]] as float32."""
+    _want(tokens, torch.int32, "tokens")
+    _want(out, torch.float32, "the residual stream")
+    vocab, width = table.shape
+    _call("frb_embed_rows", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), tokens.numel(), width, vocab)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            out32: Optional[torch.Tensor] = None, write_back: bool = False) -> None:
+    """out[r] = rmsnorm(x[src] + delta[src]) * weight with src = rows[r] (or r); the sum is stored back
+    into x when write_back."""
+    _want(x, torch.float32, "the residual stream")
+    if delta is not None:
+        _want(delta, torch.float32, "the residual update")
+    if rows is not None:
+        _want(rows, torch.int32, "row indices")
+    if out32 is not None:
+        _want(out32, torch.float32, "the 32-bit copy")
+    num_rows = rows.numel() if rows is not None else x.shape[0]
+    width = x.shape[-1]
+    _call("frb_rmsnorm", _ptr(x), _ptr(delta), _ptr(rows), _ptr(weight), _code(weight.dtype), float(eps), num_rows, width,
+          _ptr(out), _code(out.dtype), _ptr(out32), int(write_back))
+
+
+def add_rows(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _want(x, torch.float32, "the residual stream")
+    _want(delta, torch.float32, "the residual update")
+    _call("frb_add_rows", _ptr(x), _ptr(delta), x.numel())
+
+
+def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                cos_table: Optional[torch.Tensor], sin_table: Optional[torch.Tensor], tok_pos: torch.Tensor,
+                tok_slot: torch.Tensor, page_table: Optional[torch.Tensor], q_out: torch.Tensor,
+                k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], *, num_heads: int,
+                num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, write_cache: bool) -> None:
+    """Full-width Q/K RMSNorm (when weights are given), rotary from the tables, Q out, K/V into their pages."""
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("q and k norm weights come together or not at all")
+    wdtype = q_weight.dtype if q_weight is not None else torch.float32
+    if k_weight is not None and k_weight.dtype != wdtype:
+        raise KernelError("q and k norm weights must have one dtype")
+    if write_cache and (k_pages is None or v_pages is None or page_table is None):
+        raise KernelError("a cache write needs pages and a page table")
+    table_positions = cos_table.shape[0] if cos_table is not None else 0
+    max_pages = page_table.shape[1] if page_table is not None else 0
+    out_dtype = q_out.dtype
+    if k_pages is not None and k_pages.dtype != out_dtype:
+        raise KernelError("queries and cache must have one dtype")
+    _call("frb_qkv_prepare", _ptr(qkv), _code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _code(wdtype), float(eps),
+          _ptr(cos_table), _ptr(sin_table), table_positions, _ptr(tok_pos), _ptr(tok_slot), _ptr(page_table), max_pages,
+          _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(out_dtype), qkv.shape[0], num_heads, num_kv_heads, head_dim,
+          rotary_dim, int(interleaved), int(write_cache))
+
+
+def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                      tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int,
+                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+    if k_pages.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("queries, cache and output must have one dtype")
+    _call("frb_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q.dtype), _ptr(page_table),
+          page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q.shape[0], num_heads, num_kv_heads, head_dim,
+          float(scale), int(window or 0))
+
+
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,
+                ids: torch.Tensor, weights: torch.Tensor) -> None:
+    _want(logits, torch.float32, "router logits")
+    if bias is not None:
+        _want(bias, torch.float32, "the routing bias")
+    _want(ids, torch.int32, "expert ids")
+    _want(weights, torch.float32, "expert weights")
+    tokens, experts = logits.shape
+    _call("frb_router_topk", _ptr(logits), _ptr(bias), tokens, experts, top_k, int(renormalize), float(routed_scale),
+          _ptr(ids), _ptr(weights))
+
+
+def expert_plan(ids: torch.Tensor, num_experts: int, tile_rows: int, counts: torch.Tensor, offsets: torch.Tensor,
+                sorted_token: torch.Tensor, row_of_assign: torch.Tensor, tile_expert: torch.Tensor,
+                tile_row0: torch.Tensor, num_tiles: torch.Tensor) -> None:
+    tokens, top_k = ids.shape
+    for t in (ids, counts, offsets, sorted_token, row_of_assign, tile_expert, tile_row0, num_tiles):
+        _want(t, torch.int32, "expert plan buffers")
+    _call("frb_expert_plan", _ptr(ids), tokens, top_k, num_experts, tile_rows, _ptr(counts), _ptr(offsets),
+          _ptr(sorted_token), _ptr(row_of_assign), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles))
+
+
+def expert_combine(y: torch.Tensor, weights: torch.Tensor, row_of_assign: torch.Tensor, out: torch.Tensor) -> None:
+    _want(y, torch.float32, "expert outputs")
+    _want(out, torch.float32, "the residual update")
+    tokens, top_k = weights.shape
+    _call("frb_expert_combine", _ptr(y), _ptr(weights), _ptr(row_of_assign), tokens, top_k, y.shape[-1], _ptr(out))
+
+
+def expert_gemm_generic(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
+                        tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
+                        out: torch.Tensor, *, paired: bool) -> None:
+    """out[row] = silu(x W1^T) * (x W3^T) (paired; w is [E, 2F, K]) or x W^T (w is [E, F, K]) per sorted row."""
+    if w.dtype != x.dtype:
+        raise KernelError("expert weights and their input must have one dtype")
+    feats = w.shape[1] // 2 if paired else w.shape[1]
+    _call("frb_expert_gemm_generic", _ptr(w), _ptr(x), _code(w.dtype), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0),
+          _ptr(num_tiles), _ptr(offsets), max_tiles, _ptr(out), _code(out.dtype), feats, w.shape[2], int(paired))
+
+
+def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    _want(logits, torch.float32, "logits")
+    _want(out, torch.int32, "picked tokens")
+    rows, vocab = logits.shape
+    _call("frb_sample_rows", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(uniform), _ptr(out))
+
+
+def gated_unit(both: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(both[:, :w]) * both[:, w:]."""
+    _want(both, torch.float32, "gate and up rows")
+    rows, width = out.shape
+    _call("frb_gated_unit", _ptr(both), _ptr(out), _code(out.dtype), rows, width)

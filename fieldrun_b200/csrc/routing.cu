@@ -1,0 +1,191 @@
+// Routing of tokens to experts: scores and top-k choice, the expert-sorted work lists that the expert
+// products run over, and the weighted sum of the experts' outputs.
+//
+// Router (src/minimax.rs:94-104): s_e = 1/(1+exp(-z_e)); choice c_e = s_e + bias_e; experts in descending c,
+// a tie going to the lower id (the reference sorts stably); the first k; weight w_e = s_e / sum of the
+// picked s.  The bias enters the choice only.  Combination (src/minimax.rs:121-123): out[t] = sum over the
+// picked experts of w * y; here always in rank order, so the sum does not depend on the batch.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- top-k choice
+
+// One warp per token.  logits [T, E] float32 -> ids [T, k] (rank order), weights [T, k].
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_experts,
+                                   int top_k, int renormalize, float routed_scale, int* __restrict__ ids,
+                                   float* __restrict__ weights) {
+    extern __shared__ float sm[];
+    float* score = sm;                    // [E]
+    float* choice = sm + num_experts;     // [E]
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* z = logits + (size_t)t * num_experts;
+    for (int e = lane; e < num_experts; e += 32) {
+        const float s = 1.0f / (1.0f + expf(-z[e]));
+        score[e] = s;
+        choice[e] = bias ? s + bias[e] : s;
+    }
+    __syncwarp();
+    float denom = 0.f;
+    for (int r = 0; r < top_k; ++r) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < num_experts; e += 32) {
+            const float c = choice[e];
+            if (c > best) { best = c; best_e = e; }      // ascending e: the first of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) {                       // nothing comparable is left (NaN scores): lowest unpicked id
+            best_e = 0;
+            while (best_e < num_experts - 1 && choice[best_e] == -INFINITY) ++best_e;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            ids[(size_t)t * top_k + r] = best_e;
+            weights[(size_t)t * top_k + r] = score[best_e];
+            choice[best_e] = -INFINITY;
+        }
+        denom += score[best_e];
+        __syncwarp();
+    }
+    if (lane == 0) {
+        for (int r = 0; r < top_k; ++r) {
+            float w = weights[(size_t)t * top_k + r];
+            if (renormalize) w = w / denom;               // s_e / sum of picked s (src/minimax.rs:100-103)
+            weights[(size_t)t * top_k + r] = w * routed_scale;
+        }
+    }
+}
+
+FRB_API int frb_router_topk(const float* logits, const float* bias, int num_tokens, int num_experts, int top_k,
+                            int renormalize, float routed_scale, int* ids, float* weights, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "router: top_k %d is outside 1..%d experts", top_k, num_experts);
+    const size_t smem = (size_t)2 * num_experts * sizeof(float);
+    FRB_CHECK_ARG(smem <= 48 * 1024, "router: %d experts exceed the kernel's 6144", num_experts);
+    router_topk_kernel<<<num_tokens, 32, smem, stream>>>(logits, bias, num_experts, top_k, renormalize, routed_scale, ids,
+                                                         weights);
+    FRB_RETURN_LAUNCH("router_topk");
+}
+
+// ----------------------------------------------------------------------------- expert-sorted work lists
+
+#define PLAN_CHUNK 1024     // assignments per block
+#define PLAN_BLOCK 256
+
+// counts[c][e] = number of assignments of chunk c that go to expert e
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_count_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int* __restrict__ counts) {
+    extern __shared__ int hist[];
+    const int c = blockIdx.x;
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) hist[e] = 0;
+    __syncthreads();
+    const int begin = c * PLAN_CHUNK, end = min(num_assign, begin + PLAN_CHUNK);
+    for (int a = begin + threadIdx.x; a < end; a += PLAN_BLOCK) atomicAdd(&hist[ids[a]], 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) counts[(size_t)c * num_experts + e] = hist[e];
+}
+
+// Turns counts into starting positions: counts[c][e] becomes the place of chunk c's first assignment to e;
+// offsets[e] the first row of expert e in the sorted list; tiles of `tile_rows` rows that never span two
+// experts are listed in (tile_expert, tile_row0) and counted in num_tiles[0].
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_scan_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int tile_rows, int* __restrict__ offsets,
+                 int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+    extern __shared__ int total[];       // [E]
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
+        int run = 0;
+        for (int c = 0; c < num_chunks; ++c) {
+            const int n = counts[(size_t)c * num_experts + e];
+            counts[(size_t)c * num_experts + e] = run;
+            run += n;
+        }
+        total[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, tiles = 0;
+        for (int e = 0; e < num_experts; ++e) {
+            offsets[e] = run;
+            for (int r = 0; r < total[e]; r += tile_rows) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = run + r;
+                ++tiles;
+            }
+            run += total[e];
+        }
+        offsets[num_experts] = run;
+        num_tiles[0] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
+        const int first = offsets[e];
+        for (int c = 0; c < num_chunks; ++c) counts[(size_t)c * num_experts + e] += first;
+    }
+}
+
+// Places every assignment a = t*k + r, in order, behind the earlier ones of the same expert.
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_fill_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int top_k, const int* __restrict__ counts,
+                 int* __restrict__ sorted_token, int* __restrict__ row_of_assign) {
+    __shared__ int chunk_ids[PLAN_CHUNK];
+    const int c = blockIdx.x;
+    const int begin = c * PLAN_CHUNK, n = min(num_assign - begin, PLAN_CHUNK);
+    for (int i = threadIdx.x; i < n; i += PLAN_BLOCK) chunk_ids[i] = ids[begin + i];
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
+        int at = counts[(size_t)c * num_experts + e];
+        for (int i = 0; i < n; ++i) {
+            if (chunk_ids[i] == e) {
+                const int a = begin + i;
+                sorted_token[at] = a / top_k;
+                row_of_assign[a] = at;
+                ++at;
+            }
+        }
+    }
+}
+
+// ids [T, k] -> offsets [E+1], sorted_token [N], row_of_assign [N], tiles.  `counts` is scratch of
+// ceil(N / 1024) * E ints.  Tile lists need room for ceil(N / tile_rows) + min(E, N) entries.
+FRB_API int frb_expert_plan(const int* ids, int num_tokens, int top_k, int num_experts, int tile_rows, int* counts,
+                            int* offsets, int* sorted_token, int* row_of_assign, int* tile_expert, int* tile_row0,
+                            int* num_tiles, cudaStream_t stream) {
+    const int num_assign = num_tokens * top_k;
+    if (num_assign == 0) return 0;
+    FRB_CHECK_ARG(num_experts * sizeof(int) <= 48 * 1024, "expert plan: %d experts exceed the kernel's 12288", num_experts);
+    const int chunks = (num_assign + PLAN_CHUNK - 1) / PLAN_CHUNK;
+    const size_t smem = (size_t)num_experts * sizeof(int);
+    plan_count_kernel<<<chunks, PLAN_BLOCK, smem, stream>>>(ids, num_assign, num_experts, counts);
+    plan_scan_kernel<<<1, PLAN_BLOCK, smem, stream>>>(counts, chunks, num_experts, tile_rows, offsets, tile_expert,
+                                                      tile_row0, num_tiles);
+    plan_fill_kernel<<<chunks, PLAN_BLOCK, 0, stream>>>(ids, num_assign, num_experts, top_k, counts, sorted_token,
+                                                        row_of_assign);
+    FRB_RETURN_LAUNCH("expert_plan");
+}
+
+// ----------------------------------------------------------------------------- weighted sum of expert outputs
+
+// out[t, :] = sum_{r < k} w[t, r] * y[row_of_assign[t*k + r], :], added in rank order.
+__global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
+                               const int* __restrict__ row_of_assign, int top_k, int width, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < top_k; ++r) {
+            const int row = row_of_assign[(size_t)t * top_k + r];
+            acc += weights[(size_t)t * top_k + r] * y[(size_t)row * width + c];
+        }
+        out[(size_t)t * width + c] = acc;
+    }
+}
+
+FRB_API int frb_expert_combine(const float* y, const float* weights, const int* row_of_assign, int num_tokens, int top_k,
+                               int width, float* out, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    combine_kernel<<<num_tokens, 256, 0, stream>>>(y, weights, row_of_assign, top_k, width, out);
+    FRB_RETURN_LAUNCH("expert_combine");
+}

@@ -1,0 +1,79 @@
+"""What one step knows besides its rows: who each token belongs to and where it sits.
+
+A step is a batch of sequences; sequence ``b`` brings ``q_len[b]`` new tokens that
+continue at position ``start[b]`` of cache slot ``slot[b]``.  The tokens of all
+sequences lie flat, one after another.  Row ``i`` of a sequence is absolute
+position ``start + i`` (src/minimax.rs:265-266, 276-278).  The same tables exist on
+the host (for decisions) and on the device (for the kernels).
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+
+class Workspace:
+    """Named scratch tensors that are kept and reused from step to step."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._store: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = (name, dtype)
+        flat = self._store.get(key)
+        if flat is None or flat.numel() < count:
+            flat = torch.empty(max(count, 1), dtype=dtype, device=self.device)
+            self._store[key] = flat
+        return flat[:count].view(*shape)
+
+    def bytes_held(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._store.values())
+
+
+class StepContext:
+    def __init__(self, workspace: Workspace, dtype: torch.dtype, slots: Sequence[int], starts: Sequence[int],
+                 q_lens: Sequence[int]):
+        self.workspace = workspace
+        self.device = workspace.device
+        self.dtype = dtype
+        self.seq_slots = [int(s) for s in slots]
+        self.seq_starts = [int(s) for s in starts]
+        self.seq_q_lens = [int(q) for q in q_lens]
+        self.num_seqs = len(self.seq_slots)
+        self.num_tokens = int(sum(self.seq_q_lens))
+        self.max_q_len = max(self.seq_q_lens, default=0)
+        self.max_kv_len = max((s + q for s, q in zip(self.seq_starts, self.seq_q_lens)), default=0)
+        self.is_decode = self.max_q_len == 1 and self.num_tokens == self.num_seqs
+        q = np.asarray(self.seq_q_lens, dtype=np.int64)
+        self.cu_q_lens = np.concatenate([[0], np.cumsum(q)]).astype(np.int32)
+        seq_of_tok = np.repeat(np.arange(self.num_seqs, dtype=np.int32), q)
+        within = np.arange(self.num_tokens, dtype=np.int64) - np.repeat(self.cu_q_lens[:-1].astype(np.int64), q)
+        pos = np.repeat(np.asarray(self.seq_starts, dtype=np.int64), q) + within
+        slot_of_tok = np.repeat(np.asarray(self.seq_slots, dtype=np.int32), q)
+        self.host_tok_pos = pos.astype(np.int32)
+        self.host_tok_seq = seq_of_tok
+        # one transfer for all the tables
+        packed = np.concatenate([
+            self.host_tok_pos, slot_of_tok, seq_of_tok,
+            np.asarray(self.seq_slots, dtype=np.int32), np.asarray(self.seq_starts, dtype=np.int32),
+            np.asarray(self.seq_q_lens, dtype=np.int32), self.cu_q_lens,
+        ]).astype(np.int32)
+        dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
+        t, b = self.num_tokens, self.num_seqs
+        self.tok_pos = dev[0:t]
+        self.tok_slot = dev[t:2 * t]
+        self.tok_seq = dev[2 * t:3 * t]
+        o = 3 * t
+        self.seq_slot = dev[o:o + b]
+        self.seq_start = dev[o + b:o + 2 * b]
+        self.seq_q_len = dev[o + 2 * b:o + 3 * b]
+        self.cu_q_len = dev[o + 3 * b:o + 4 * b + 1]
+
+    def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        return self.workspace.buffer(name, shape, dtype)

@@ -1,0 +1,2 @@
+"""Built-in architectures; importing this package registers them."""
+from . import minimax_m2  # noqa: F401

@@ -1,0 +1,110 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v = act W^T without bias; optionally one RMSNorm over the whole Q row and
+one over the whole K row ("full_width", before the head split and the rotary,
+src/minimax.rs:136-138); rotary on the first ``rotary_dim`` dims of each head at
+the token's absolute position; K (normed, rotated) and V written to the cache
+line; every query head h attends, with keys of head h // (heads / kv_heads), over
+the keys it may see; output projection without bias (src/minimax.rs:253-282).
+The three projections are held as one matrix so that one product makes q|k|v.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..cache import CacheNeed, LineView
+from ..csrc import ops
+from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
+from .base import Mixer, build_position, register_part
+from .linear import linear
+
+
+class GQAAttention(Mixer):
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        a = spec.args
+        self.hidden_size = int(a["hidden_size"])
+        self.num_heads = int(a["num_heads"])
+        self.num_kv_heads = int(a["num_kv_heads"])
+        self.head_dim = int(a["head_dim"])
+        self.qk_norm = a.get("qk_norm", "none")
+        if self.qk_norm not in ("none", "full_width"):
+            raise ValueError(f"qk_norm {self.qk_norm!r} is neither 'none' nor 'full_width'")
+        self.qk_norm_eps = float(a.get("qk_norm_eps", 1e-6))
+        self.softmax_scale = float(a.get("softmax_scale", self.head_dim ** -0.5))
+        self.window = a.get("window")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError(f"an attention window of {self.window} keys")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} kv heads")
+        if not 1 <= self.head_dim <= 256:
+            raise ValueError(f"head_dim {self.head_dim} is outside the kernels' range 1..256")
+        self.position = build_position(a.get("position"))
+        if self.position is not None and self.position.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary_dim {self.position.rotary_dim} exceeds head_dim {self.head_dim}")
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+        self.q_norm: Optional[torch.Tensor] = None
+        self.k_norm: Optional[torch.Tensor] = None
+        self.cos: Optional[torch.Tensor] = None
+        self.sin: Optional[torch.Tensor] = None
+
+    # -- tensors -----------------------------------------------------------------------------------
+    def _needs(self) -> dict[str, TensorNeed]:
+        needs = {
+            "q_proj": TensorNeed(self.name_of("q_proj"), (self.q_width, self.hidden_size), MATRIX, "normal"),
+            "k_proj": TensorNeed(self.name_of("k_proj"), (self.kv_width, self.hidden_size), MATRIX, "normal"),
+            "v_proj": TensorNeed(self.name_of("v_proj"), (self.kv_width, self.hidden_size), MATRIX, "normal"),
+            "o_proj": TensorNeed(self.name_of("o_proj"), (self.hidden_size, self.q_width), MATRIX, "normal"),
+        }
+        if self.qk_norm == "full_width":
+            needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.q_width,), VECTOR, "around_one")
+            needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.kv_width,), VECTOR, "around_one")
+        return needs
+
+    def tensor_needs(self):
+        return list(self._needs().values())
+
+    def load(self, source: TensorSource) -> None:
+        needs = self._needs()
+        self.w_qkv = torch.cat([source.fetch(needs[n]) for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
+        self.w_o = source.fetch(needs["o_proj"])
+        if self.qk_norm == "full_width":
+            self.q_norm = source.fetch(needs["q_norm"])
+            self.k_norm = source.fetch(needs["k_norm"])
+
+    # -- cache and tables ----------------------------------------------------------------------------
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                         window=int(self.window) if self.window is not None else None)
+
+    def prepare(self, num_positions: int, device) -> None:
+        if self.position is not None and self.position.rotary_dim > 0:
+            self.cos, self.sin = self.position.tables(num_positions, device)
+
+    # -- one step --------------------------------------------------------------------------------------
+    def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
+        tokens = act.shape[0]
+        qkv = linear(act, self.w_qkv)                                        # float32 [T, q + 2 kv]
+        q = ctx.buffer("attention.q", (tokens, self.q_width), self.dtype)
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        ops.qkv_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps, self.cos, self.sin, ctx.tok_pos, ctx.tok_slot,
+                        line.page_table, q, line.keys, line.values, num_heads=self.num_heads,
+                        num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=rotary_dim,
+                        interleaved=bool(self.position.interleaved) if self.position is not None else False,
+                        write_cache=writes_cache)
+        out = ctx.buffer("attention.out", (tokens, self.q_width), self.dtype)
+        self.attend(ctx, q, line, out)
+        return linear(out, self.w_o)
+
+    def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor) -> None:
+        ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
+                              num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                              scale=self.softmax_scale, window=self.window)
+
+
+register_part("mixer", "gqa_attention", GQAAttention, replace=True)

@@ -1,0 +1,158 @@
+"""Feed-forward parts: experts chosen by a router, and a dense gated unit.
+
+Routed experts (src/minimax.rs:88-126): router logits z = act W_r^T in float32;
+score s = sigmoid(z); choice c = s + bias (the bias decides only who is picked);
+the ``top_k`` largest c, ties to the lower id; weights s / sum of the picked s;
+each picked expert computes silu(x W1^T) * (x W3^T) then W2; the outputs are
+summed with their weights in rank order.  The experts' matrices are stacked:
+``w13`` [E, 2I, d] holds each expert's gate rows then its up rows, ``w2`` [E, d, I].
+Rows are grouped by expert with a counting sort on the device, so no step of the
+feed-forward waits for the host.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
+from .base import FeedForward, register_part
+from .linear import linear
+
+TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
+
+
+class RoutedExperts(FeedForward):
+    wants_float32_input = True          # the router reads the normed rows before they are rounded
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        a = spec.args
+        self.hidden_size = int(a["hidden_size"])
+        self.num_experts = int(a["num_experts"])
+        self.top_k = int(a["top_k"])
+        self.expert_width = int(a["expert_width"])
+        if a.get("score", "sigmoid") != "sigmoid":
+            raise ValueError(f"router score {a.get('score')!r}: only 'sigmoid' is built")
+        self.choice_bias = bool(a.get("choice_bias", False))
+        self.renormalize = bool(a.get("renormalize", True))
+        self.routed_scale = float(a.get("routed_scale", 1.0))
+        if not 1 <= self.top_k <= self.num_experts:
+            raise ValueError(f"top_k {self.top_k} is outside 1..{self.num_experts} experts")
+        self.router: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.w13: Optional[torch.Tensor] = None
+        self.w2: Optional[torch.Tensor] = None
+
+    def _expert_needs(self, e: int) -> tuple[TensorNeed, TensorNeed, TensorNeed]:
+        d, i = self.hidden_size, self.expert_width
+        return (TensorNeed(self.name_of("w_gate").format(e=e), (i, d), MATRIX, "normal"),
+                TensorNeed(self.name_of("w_up").format(e=e), (i, d), MATRIX, "normal"),
+                TensorNeed(self.name_of("w_down").format(e=e), (d, i), MATRIX, "normal"))
+
+    def tensor_needs(self):
+        needs = [TensorNeed(self.name_of("router"), (self.num_experts, self.hidden_size), VECTOR, "normal")]
+        if self.choice_bias:
+            needs.append(TensorNeed(self.name_of("choice_bias"), (self.num_experts,), VECTOR, "bias"))
+        for e in range(self.num_experts):
+            needs.extend(self._expert_needs(e))
+        return needs
+
+    def load(self, source: TensorSource) -> None:
+        d, i, n = self.hidden_size, self.expert_width, self.num_experts
+        self.router = source.fetch(TensorNeed(self.name_of("router"), (n, d), VECTOR, "normal"))
+        if self.choice_bias:
+            self.bias = source.fetch(TensorNeed(self.name_of("choice_bias"), (n,), VECTOR, "bias"))
+        for e in range(n):
+            gate, up, down = (source.fetch(need) for need in self._expert_needs(e))
+            if self.w13 is None:
+                self.w13 = torch.empty((n, 2 * i, d), dtype=gate.dtype, device=gate.device)
+                self.w2 = torch.empty((n, d, i), dtype=gate.dtype, device=gate.device)
+            self.w13[e, :i].copy_(gate)
+            self.w13[e, i:].copy_(up)
+            self.w2[e].copy_(down)
+
+    # -- one step --------------------------------------------------------------------------------------
+    def route(self, ctx, act32: torch.Tensor):
+        tokens = act32.shape[0]
+        logits = linear(act32, self.router)                       # float32 rows, float32 weight: no rounding
+        ids = ctx.buffer("experts.ids", (tokens, self.top_k), torch.int32)
+        weights = ctx.buffer("experts.weights", (tokens, self.top_k), torch.float32)
+        ops.router_topk(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, ids, weights)
+        return ids, weights
+
+    def plan(self, ctx, ids: torch.Tensor):
+        tokens = ids.shape[0]
+        n = tokens * self.top_k
+        chunks = (n + 1023) // 1024
+        max_tiles = (n + TILE_ROWS - 1) // TILE_ROWS + min(self.num_experts, n)
+        p = {
+            "counts": ctx.buffer("experts.counts", (chunks * self.num_experts,), torch.int32),
+            "offsets": ctx.buffer("experts.offsets", (self.num_experts + 1,), torch.int32),
+            "sorted_token": ctx.buffer("experts.sorted_token", (n,), torch.int32),
+            "row_of_assign": ctx.buffer("experts.row_of_assign", (n,), torch.int32),
+            "tile_expert": ctx.buffer("experts.tile_expert", (max_tiles,), torch.int32),
+            "tile_row0": ctx.buffer("experts.tile_row0", (max_tiles,), torch.int32),
+            "num_tiles": ctx.buffer("experts.num_tiles", (1,), torch.int32),
+            "max_tiles": max_tiles,
+            "rows": n,
+        }
+        ops.expert_plan(ids, self.num_experts, TILE_ROWS, p["counts"], p["offsets"], p["sorted_token"],
+                        p["row_of_assign"], p["tile_expert"], p["tile_row0"], p["num_tiles"])
+        return p
+
+    def experts(self, ctx, act: torch.Tensor, p) -> torch.Tensor:
+        """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order."""
+        hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
+        ops.expert_gemm_generic(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
+                                p["offsets"], p["max_tiles"], hidden, paired=True)
+        y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
+        ops.expert_gemm_generic(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                                p["max_tiles"], y, paired=False)
+        return y
+
+    def forward(self, ctx, act, act32):
+        if act32 is None:
+            raise ValueError("routed experts need the normed rows in float32 for the router")
+        ids, weights = self.route(ctx, act32)
+        p = self.plan(ctx, ids)
+        y = self.experts(ctx, act, p)
+        out = ctx.buffer("experts.out", (act.shape[0], self.hidden_size), torch.float32)
+        ops.expert_combine(y, weights, p["row_of_assign"], out)
+        return out
+
+
+class DenseGatedUnit(FeedForward):
+    """silu(x W_gate^T) * (x W_up^T), then W_down: one expert's formula for every row (src/minimax.rs:116-120)."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.hidden_size = int(spec.args["hidden_size"])
+        self.width = int(spec.args["width"])
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def _needs(self):
+        d, i = self.hidden_size, self.width
+        return (TensorNeed(self.name_of("w_gate"), (i, d), MATRIX, "normal"),
+                TensorNeed(self.name_of("w_up"), (i, d), MATRIX, "normal"),
+                TensorNeed(self.name_of("w_down"), (d, i), MATRIX, "normal"))
+
+    def tensor_needs(self):
+        return list(self._needs())
+
+    def load(self, source: TensorSource) -> None:
+        gate, up, down = (source.fetch(n) for n in self._needs())
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = down
+
+    def forward(self, ctx, act, act32):
+        both = linear(act, self.w_gate_up)                         # float32 [T, 2I]
+        hidden = ctx.buffer("dense.hidden", (act.shape[0], self.width), self.dtype)
+        ops.gated_unit(both, hidden)
+        return linear(hidden, self.w_down)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
+register_part("feed_forward", "dense_gated", DenseGatedUnit, replace=True)
