@@ -125,6 +125,12 @@ def build(verbose: bool = True, ptxas_info: bool = False) -> str:
     if proc.returncode != 0:
         raise BuildError(f"linking the kernels failed:\n{proc.stdout}\n{proc.stderr}")
     os.replace(partial, target)
+    for name in os.listdir(out_dir):                       # libraries of older sources
+        if name.startswith("libfieldrun_b200_") and name.endswith(".so") and name != os.path.basename(target):
+            try:
+                os.remove(os.path.join(out_dir, name))
+            except OSError:
+                pass
     for obj in objects:
         try:
             os.remove(obj)

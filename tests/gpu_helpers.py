@@ -1,0 +1,87 @@
+"""Shared pieces of the GPU tests: model folders in temporary places, plain logits, comparisons."""
+import functools
+import os
+import tempfile
+
+import numpy as np
+
+import fieldrun_b200 as fr
+import plain_model as pm
+from tiny_configs import ALL
+
+# largest allowed |engine - plain| as a share of the largest |plain logit| of the compared rows
+TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+_ROOT = tempfile.mkdtemp(prefix="fieldrun_b200_tests_")
+
+
+@functools.lru_cache(maxsize=None)
+def model_folder(name: str) -> str:
+    config, init = ALL[name]
+    folder = os.path.join(_ROOT, name)
+    fr.write_random_model(folder, config, init)
+    return folder
+
+
+@functools.lru_cache(maxsize=None)
+def plain_weights(name: str):
+    return pm.read_model_folder(model_folder(name))
+
+
+def request_tokens(name: str, length: int, seed: int) -> list[int]:
+    vocab = ALL[name][0]["vocab_size"]
+    return np.random.default_rng(1000 * seed + length).integers(0, vocab, size=length).tolist()
+
+
+@functools.lru_cache(maxsize=None)
+def _plain_run(name: str, length: int, seed: int):
+    config, weights = plain_weights(name)
+    s = pm.sizes_from_config(config)
+    hidden, margins = pm.hidden_states(config, weights, request_tokens(name, length, seed), return_margins=True)
+    head = weights["model.embed_tokens.weight"] if s["tied"] else weights["lm_head.weight"]
+    return hidden @ head.astype(np.float64).T, margins.min(axis=0)
+
+
+def plain_logits(name: str, length: int, seed: int) -> np.ndarray:
+    return _plain_run(name, length, seed)[0]
+
+
+def plain_margins(name: str, length: int, seed: int) -> np.ndarray:
+    """Per token, the smallest gap over the layers between the last picked expert's choice value and the
+    first one left out.  Where it is tiny, rounding may pick another expert: the router is not continuous."""
+    return _plain_run(name, length, seed)[1]
+
+
+def worst(got, ref) -> float:
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert np.isfinite(got).all(), "the engine produced a non-finite logit"
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+# A token whose router margin is below this may get another expert under bfloat16 rounding (the noise of a
+# choice value there is about 2e-4); its row, and only its row, is then held to NEAR_TIE_FACTOR x the tolerance.
+NEAR_TIE_MARGIN = {"float32": 1e-6, "bfloat16": 1.5e-3}
+NEAR_TIE_FACTOR = 4.0
+
+
+def assert_close(got, ref, dtype: str, what: str = "", margins=None) -> None:
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    worst(got, ref)
+    per_row = np.abs(got - ref).max(axis=-1) / max(np.abs(ref).max(), 1e-30)
+    limit = np.full(len(per_row), TOLERANCE[dtype])
+    if margins is not None:
+        limit[np.asarray(margins) < NEAR_TIE_MARGIN[dtype]] *= NEAR_TIE_FACTOR
+    bad = per_row > limit
+    if bad.any():
+        first = int(np.argmax(bad))
+        margin = f", router margin there {margins[first]:.2e}" if margins is not None else ""
+        raise AssertionError(f"{what}: relative error {per_row[first]:.3e} exceeds {limit[first]:.1e} ({dtype}); "
+                             f"first wrong row {first} of {len(per_row)}{margin}; row errors {np.round(per_row[:40], 6)}")
+
+
+@functools.lru_cache(maxsize=None)
+def loaded(name: str, dtype: str, max_tokens: int = 2048, num_slots=None):
+    return fr.load(model_folder(name), dtype=dtype, max_tokens=max_tokens, num_slots=num_slots)

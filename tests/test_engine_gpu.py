@@ -1,0 +1,199 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: whole requests, the last
+tokens one by one, batches of unequal lengths through few slots, long decoding, the first tokens."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+from gpu_helpers import (TOLERANCE, assert_close, loaded, model_folder, plain_logits, plain_margins, plain_weights,
+                         request_tokens, worst)
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+NAMES = list(ALL)
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = [1, 5, 13, 40, 64, 77, 130]
+
+
+def to_np(t):
+    return t.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(name, dtype):
+    lm = loaded(name, dtype)
+    for length in LENGTHS:
+        ids = request_tokens(name, length, 0)
+        got = to_np(lm.logits(ids))
+        assert_close(got, plain_logits(name, length, 0), dtype, f"{name} whole request of {length}",
+                     plain_margins(name, length, 0))
+    lm.engine.cache.check()
+    assert lm.engine.cache.slots.num_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(name, dtype):
+    lm = loaded(name, dtype)
+    engine = lm.engine
+    for length in (40, 77, 130):
+        ids = request_tokens(name, length, 0)
+        ref = plain_logits(name, length, 0)
+        head = length - 32
+        slot = engine.new_sequence()
+        try:
+            rows = [to_np(engine.step([slot], [ids[:head]], [list(range(head))]))]
+            for i in range(head, length):
+                rows.append(to_np(engine.step([slot], [[ids[i]]], [[0]])))
+        finally:
+            engine.release(slot)
+        assert_close(np.concatenate(rows), ref, dtype, f"{name} length {length}, last 32 one by one",
+                     plain_margins(name, length, 0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_through_few_slots(name, dtype):
+    """Three slots, seven requests: prompts of a batch in one step, then one token each, the shorter
+    ones leaving earlier; the next batch takes the freed slots."""
+    lm = loaded(name, dtype, 2048, 3)
+    engine = lm.engine
+    plan = [(130, 9), (5, 2), (77, 20), (1, 0), (64, 33), (40, 39), (13, 5)]      # (length, decoded at the end)
+    for start in range(0, len(plan), 3):
+        batch = plan[start:start + 3]
+        slots = [engine.new_sequence() for _ in batch]
+        ids = [request_tokens(name, length, 0) for length, _ in batch]
+        got = [[] for _ in batch]
+        heads = [length - dec for length, dec in batch]
+        out = to_np(engine.step(slots, [i[:h] for i, h in zip(ids, heads)], [list(range(h)) for h in heads]))
+        at = 0
+        for b, h in enumerate(heads):
+            got[b].append(out[at:at + h])
+            at += h
+        step = 0
+        while True:
+            live = [b for b, (length, dec) in enumerate(batch) if step < dec]
+            if not live:
+                break
+            out = to_np(engine.step([slots[b] for b in live], [[ids[b][heads[b] + step]] for b in live]))
+            for row, b in enumerate(live):
+                got[b].append(out[row:row + 1])
+            step += 1
+        for slot in slots:
+            engine.release(slot)
+        engine.cache.check()
+        for b, (length, dec) in enumerate(batch):
+            assert_close(np.concatenate(got[b]), plain_logits(name, length, 0), dtype,
+                         f"{name} batch at {start}, request of {length} with {dec} decoded",
+                         plain_margins(name, length, 0))
+    assert engine.cache.slots.num_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(dtype):
+    name = "a"
+    lm = loaded(name, dtype)
+    engine = lm.engine
+    length = 230
+    ids = request_tokens(name, length, 3)
+    ref = plain_logits(name, length, 3)
+    slot = engine.new_sequence()
+    try:
+        rows = [to_np(engine.step([slot], [[t]], [[0]])) for t in ids]       # from the very first token
+    finally:
+        engine.release(slot)
+    got = np.concatenate(rows)
+    assert_close(got[:3], ref[:3], dtype, "the first tokens", plain_margins(name, length, 3)[:3])
+    assert_close(got, ref, dtype, "230 tokens one by one", plain_margins(name, length, 3))
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_padding_and_company_change_nothing(name):
+    """The same request alone, and beside others of other lengths, in float32: the same logits up to rounding."""
+    lm = loaded(name, "float32")
+    engine = lm.engine
+    ids = request_tokens(name, 40, 0)
+    alone = to_np(lm.logits(ids))
+    others = [request_tokens(name, n, 1) for n in (3, 90)]
+    slots = [engine.new_sequence() for _ in range(3)]
+    try:
+        out = to_np(engine.step(slots, [others[0], ids, others[1]], [[], list(range(40)), []]))
+    finally:
+        for s in slots:
+            engine.release(s)
+    assert worst(out, alone) < 2e-6
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_entry_point(name):
+    lm = loaded(name, "float32")
+    config, weights = plain_weights(name)
+    prompt = request_tokens(name, 9, 2)
+    want = pm.generate_greedy(config, weights, prompt, 12)
+    assert lm.generate(prompt, 12) == want
+    assert lm.predict(prompt) == want[0]
+    stop = want[4]
+    cut = want[:want.index(stop)]
+    assert lm.generate_stream(prompt, 12, eos=[stop]) == cut
+    seen = []
+    assert lm.generate_stream(prompt, 12, emit=lambda t: (seen.append(t), len(seen) < 3)[1]) == want[:3]
+    prompts = [request_tokens(name, n, 2) for n in (9, 2, 30, 17)]
+    outs, reasons = lm.generate_batch(prompts, 6, eos=[], return_reasons=True)
+    assert outs == [pm.generate_greedy(config, weights, p, 6) for p in prompts] and reasons == ["length"] * 4
+    lm.engine.cache.check()
+    assert lm.engine.cache.slots.num_held == 0
+
+
+def test_greedy_generation_in_bfloat16_stays_on_the_plain_models_top():
+    name = "b"
+    lm = loaded(name, "bfloat16")
+    config, weights = plain_weights(name)
+    prompt = request_tokens(name, 20, 2)
+    out = lm.generate(prompt, 16)
+    ref = pm.logits_all_positions(config, weights, prompt + out)
+    for i, token in enumerate(out):
+        row = ref[len(prompt) - 1 + i]
+        assert row[token] >= row.max() - 2 * TOLERANCE["bfloat16"] * np.abs(ref).max()
+
+
+def test_temperature_sampling_repeats_with_its_seed_and_follows_the_plain_pick():
+    from fieldrun_b200.sampling import uniform
+    name = "a"
+    lm = loaded(name, "float32")
+    config, weights = plain_weights(name)
+    prompts = [request_tokens(name, n, 4) for n in (6, 11)]
+    first = lm.generate_batch(prompts, 10, eos=[], temperature=0.8, seed=5)
+    assert first == lm.generate_batch(prompts, 10, eos=[], temperature=0.8, seed=5)
+    assert first != lm.generate_batch(prompts, 10, eos=[], temperature=0.8, seed=6)
+    for index, (prompt, out) in enumerate(zip(prompts, first)):
+        seq = list(prompt)
+        for step, token in enumerate(out):
+            row = pm.logits_all_positions(config, weights, seq)[-1]
+            assert token == pm.temperature_pick(row, 0.8, uniform(5, index, step))
+            seq.append(token)
+
+
+def test_errors_come_before_any_launch():
+    from fieldrun_b200.cache import CacheFull
+    from fieldrun_b200.engine import StepError
+    lm = loaded("a", "float32", 2048, 3)
+    engine = lm.engine
+    slot = engine.new_sequence()
+    try:
+        with pytest.raises(StepError, match="outside the vocabulary"):
+            engine.step([slot], [[1, 256]])
+        with pytest.raises(StepError, match="wanted place"):
+            engine.step([slot], [[1, 2]], [[2]])
+        with pytest.raises(StepError, match="position tables end"):
+            engine.step([slot], [[1] * 2049])
+        other = engine.new_sequence()
+        with pytest.raises(CacheFull, match="pages"):
+            engine.step([slot, other], [[1] * 1500, [2] * 600])
+        engine.release(other)
+        assert engine.length(slot) == 0
+        assert engine.step([slot], [[1, 2, 3]], [[]]) is None and engine.length(slot) == 3
+    finally:
+        engine.release(slot)
+    engine.cache.check()

@@ -1,0 +1,350 @@
+"""Each kernel alone against a plain numpy reference, at sizes other than the tiny models'."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from fieldrun_b200.csrc import ops as o
+    return o
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(DEV).contiguous()
+
+
+def f64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def bf16_round(a):
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 3e-6, "bfloat16": 1e-2}
+
+
+def close(got, ref, tol, what=""):
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert np.isfinite(got).all(), what
+    err = np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)
+    assert err <= tol, f"{what}: relative error {err:.3e} > {tol:.1e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_rows(dtype):
+    rng = np.random.default_rng(0)
+    table = dev(rng.normal(size=(1000, 100)), TORCH[dtype])
+    tokens = rng.integers(0, 1000, size=37)
+    out = torch.empty(37, 100, dtype=torch.float32, device=DEV)
+    ops().embed_rows(dev(tokens, torch.int32), table, out)
+    np.testing.assert_array_equal(f64(out), f64(table)[tokens])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [100, 3072, 5000])
+def test_rmsnorm_with_residual_sum_rows_and_float32_copy(dtype, width):
+    rng = np.random.default_rng(1)
+    x, delta, w = rng.normal(size=(9, width)), rng.normal(size=(9, width)), 1 + 0.1 * rng.normal(size=width)
+    x32, d32, w32 = (np.asarray(a, dtype=np.float32) for a in (x, delta, w))
+    ref_sum = x32.astype(np.float64) + d32.astype(np.float64)
+    ref = pm.rms_norm(ref_sum, w32.astype(np.float64), 1e-5)
+    xd = dev(x32)
+    out = torch.empty(9, width, dtype=TORCH[dtype], device=DEV)
+    out32 = torch.empty(9, width, dtype=torch.float32, device=DEV)
+    ops().rmsnorm(xd, dev(w32), 1e-5, out, delta=dev(d32), out32=out32, write_back=True)
+    close(f64(out), ref, TOL[dtype], "normed rows")
+    close(f64(out32), ref, 3e-6, "float32 copy")
+    close(f64(xd), ref_sum, 1e-6, "the stream holds the sum")
+    rows = np.array([7, 0, 3], dtype=np.int32)
+    xd2 = dev(x32)
+    picked = torch.empty(3, width, dtype=TORCH[dtype], device=DEV)
+    ops().rmsnorm(xd2, dev(w32), 1e-5, picked, delta=dev(d32), rows=dev(rows), write_back=False)
+    close(f64(picked), ref[rows], TOL[dtype], "picked rows")
+    np.testing.assert_array_equal(f64(xd2), x32.astype(np.float64))          # untouched without write_back
+    plain = torch.empty(9, width, dtype=TORCH[dtype], device=DEV)
+    ops().rmsnorm(xd2, dev(w32), 1e-5, plain)
+    close(f64(plain), pm.rms_norm(x32.astype(np.float64), w32.astype(np.float64), 1e-5), TOL[dtype], "no delta")
+
+
+def paged_cache(rng, slots, pages, kv_heads, head_dim, dtype):
+    """A cache whose pages are handed out in a scrambled order, filled with junk where nothing was written."""
+    order = rng.permutation(pages)
+    keys = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)) * 5, TORCH[dtype])
+    values = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)) * 5, TORCH[dtype])
+    table = np.full((slots, pages), -1, dtype=np.int32)
+    return keys, values, table, list(order)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,normed,interleaved", [
+    (6, 2, 32, 16, True, False), (5, 5, 24, 24, False, False), (8, 1, 128, 64, True, False),
+    (4, 2, 16, 8, True, True), (3, 3, 20, 0, True, False)])
+def test_qk_norm_rotary_and_cache_write(dtype, heads, kv_heads, head_dim, rotary, normed, interleaved):
+    from fieldrun_b200.parts.position import Rotary
+    rng = np.random.default_rng(2)
+    T = 11
+    qw, kw = heads * head_dim, kv_heads * head_dim
+    qkv = rng.normal(size=(T, qw + 2 * kw)).astype(np.float32)
+    wq = (1 + 0.2 * rng.normal(size=qw)).astype(np.float32)
+    wk = (1 + 0.2 * rng.normal(size=kw)).astype(np.float32)
+    positions = np.array([0, 1, 2, 63, 64, 65, 130, 5, 6, 7, 191], dtype=np.int32)
+    slot_of = np.array([0, 0, 0, 0, 0, 0, 0, 2, 2, 2, 2], dtype=np.int32)
+    keys, values, table, free = paged_cache(rng, 3, 12, kv_heads, head_dim, dtype)
+    for slot, need in ((0, 3), (2, 3)):
+        for i in range(need):
+            table[slot, i] = free.pop()
+    cos = sin = None
+    if rotary:
+        cos, sin = Rotary({"rotary_dim": rotary, "theta": 1234.5, "pairing": "interleaved" if interleaved else "half"}).tables(256, DEV)
+    q_out = torch.empty(T, qw, dtype=TORCH[dtype], device=DEV)
+    ops().qkv_prepare(dev(qkv), dev(wq) if normed else None, dev(wk) if normed else None, 1e-5, cos, sin,
+                      dev(positions), dev(slot_of), dev(table), q_out, keys, values, num_heads=heads,
+                      num_kv_heads=kv_heads, head_dim=head_dim, rotary_dim=rotary, interleaved=interleaved, write_cache=True)
+    q, k, v = (qkv[:, :qw].astype(np.float64), qkv[:, qw:qw + kw].astype(np.float64), qkv[:, qw + kw:].astype(np.float64))
+    if normed:
+        q, k = pm.rms_norm(q, wq.astype(np.float64), 1e-5), pm.rms_norm(k, wk.astype(np.float64), 1e-5)
+
+    def rotate(x, n):
+        if not rotary:
+            return x
+        if not interleaved:
+            return pm.rotary(x, n, head_dim, rotary, 1234.5, positions)
+        out = x.copy()
+        inv = pm.rotary_inverse_frequencies(1234.5, rotary, np.float64)
+        ang = positions.astype(np.float64)[:, None] * inv[None, :]
+        for h in range(n):
+            a, b = x[:, h * head_dim:h * head_dim + rotary:2], x[:, h * head_dim + 1:h * head_dim + rotary:2]
+            out[:, h * head_dim:h * head_dim + rotary:2] = a * np.cos(ang) - b * np.sin(ang)
+            out[:, h * head_dim + 1:h * head_dim + rotary:2] = b * np.cos(ang) + a * np.sin(ang)
+        return out
+
+    q, k = rotate(q, heads), rotate(k, kv_heads)
+    close(f64(q_out), q, TOL[dtype], "queries")
+    kc, vc = f64(keys), f64(values)
+    for t in range(T):
+        page = table[slot_of[t], positions[t] // 64]
+        close(kc[page, :, positions[t] % 64, :].reshape(-1), k[t], TOL[dtype], f"key of token {t}")
+        close(vc[page, :, positions[t] % 64, :].reshape(-1), v[t], TOL[dtype], f"value of token {t}")
+
+
+def reference_attention(q, kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window):
+    out = np.zeros((len(positions), heads * head_dim))
+    rep = heads // kv_heads
+    for t, (pos, slot) in enumerate(zip(positions, slot_of)):
+        lo = max(0, pos - window + 1) if window else 0
+        js = np.arange(lo, pos + 1)
+        for h in range(heads):
+            g = h // rep
+            k = np.stack([kc[table[slot, j // 64], g, j % 64] for j in js])
+            v = np.stack([vc[table[slot, j // 64], g, j % 64] for j in js])
+            s = (k @ q[t, h * head_dim:(h + 1) * head_dim]) * scale
+            p = np.exp(s - s.max())
+            out[t, h * head_dim:(h + 1) * head_dim] = (p / p.sum()) @ v
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 2, 32, None), (9, 1, 24, None), (4, 4, 128, 70),
+                                                            (12, 2, 80, None), (20, 2, 16, 33)])
+def test_attention_over_scrambled_pages(dtype, heads, kv_heads, head_dim, window):
+    rng = np.random.default_rng(3)
+    lengths = {0: 200, 1: 65, 3: 1}
+    keys, values, table, free = paged_cache(rng, 4, 10, kv_heads, head_dim, dtype)
+    kc, vc = f64(keys), f64(values)
+    for slot, n in lengths.items():
+        for i in range((n + 63) // 64):
+            table[slot, i] = free.pop()
+    positions = np.array([199, 198, 130, 64, 63, 0, 64, 10, 0], dtype=np.int32)
+    slot_of = np.array([0, 0, 0, 0, 0, 0, 1, 1, 3], dtype=np.int32)
+    q = rng.normal(size=(len(positions), heads * head_dim))
+    qd = dev(q, TORCH[dtype])
+    out = torch.empty_like(qd)
+    scale = 0.1
+    ops().attention_generic(qd, keys, values, dev(table), dev(positions), dev(slot_of), out, num_heads=heads,
+                            num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+    ref = reference_attention(f64(qd), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
+    close(f64(out), ref, TOL[dtype], "attention")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_and_respects_the_windows_edge(dtype):
+    """All keys are tiny except one far back whose score stands out: the output must be that key's value.
+    With a window that ends one key short of it, the output must not contain it at all."""
+    rng = np.random.default_rng(4)
+    heads, kv_heads, head_dim, n = 4, 2, 32, 700
+    pages = (n + 63) // 64
+    keys = torch.zeros(pages, kv_heads, 64, head_dim, dtype=TORCH[dtype], device=DEV)
+    values = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)), TORCH[dtype])
+    table = np.arange(pages, dtype=np.int32)[::-1].copy()[None, :]
+    far = 37
+    page, row = table[0, far // 64], far % 64
+    keys[page, :, row, :] = 1.0
+    q = np.full((1, heads * head_dim), 4.0)
+    positions, slot_of = np.array([n - 1], dtype=np.int32), np.array([0], dtype=np.int32)
+    out = torch.empty(1, heads * head_dim, dtype=TORCH[dtype], device=DEV)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=1.0)
+    ops().attention_generic(dev(q, TORCH[dtype]), keys, values, dev(table), dev(positions), dev(slot_of), out, window=None, **args)
+    want = np.repeat(f64(values)[page, :, row, :], heads // kv_heads, axis=0).reshape(1, -1)
+    close(f64(out), want, 1e-5 if dtype == "float32" else 1e-2, "the far key")
+    for window, inside in ((n - far, True), (n - far - 1, False)):
+        ops().attention_generic(dev(q, TORCH[dtype]), keys, values, dev(table), dev(positions), dev(slot_of), out, window=window, **args)
+        if inside:
+            close(f64(out), want, 1e-5 if dtype == "float32" else 1e-2, "the far key at the window's edge")
+        else:
+            mean = np.stack([f64(values)[table[0, j // 64], :, j % 64, :] for j in range(far + 1, n)]).mean(0)
+            close(f64(out), np.repeat(mean, heads // kv_heads, axis=0).reshape(1, -1), 2e-5 if dtype == "float32" else 2e-2,
+                  "one key past the window's edge")
+
+
+@pytest.mark.parametrize("experts,top_k,biased", [(256, 8, True), (5, 1, False), (37, 4, True), (8, 8, True)])
+def test_router_choice_and_weights(experts, top_k, biased):
+    rng = np.random.default_rng(5)
+    logits = rng.normal(size=(50, experts)).astype(np.float32)
+    logits[3] = 0.0                                              # every score equal: ties go to the lower id
+    logits[4, :] = np.repeat(rng.normal(size=(experts + 1) // 2), 2)[:experts]       # pairs of equal scores
+    bias = (0.3 * rng.normal(size=experts)).astype(np.float32) if biased else None
+    if biased:
+        bias[:] = np.round(bias, 2)
+    ids = torch.empty(50, top_k, dtype=torch.int32, device=DEV)
+    weights = torch.empty(50, top_k, dtype=torch.float32, device=DEV)
+    ops().router_topk(dev(logits), dev(bias) if biased else None, top_k, True, 1.0, ids, weights)
+    score = (1.0 / (1.0 + np.exp(-logits.astype(np.float32)))).astype(np.float32)
+    choice = score + bias if biased else score
+    order = np.argsort(-choice, axis=-1, kind="stable")[:, :top_k]
+    got_ids = ids.cpu().numpy()
+    ranked = np.take_along_axis(choice, np.argsort(-choice, axis=-1, kind="stable"), -1)
+    clear = np.ones(50, dtype=bool) if experts == top_k else (ranked[:, top_k - 1] - ranked[:, top_k] > 1e-6)
+    clear[3] = clear[4] = True                                    # exact ties must follow the rule
+    np.testing.assert_array_equal(got_ids[clear], order[clear])
+    picked = np.take_along_axis(score.astype(np.float64), got_ids.astype(np.int64), -1)
+    close(f64(weights), picked / picked.sum(-1, keepdims=True), 2e-6, "weights")
+    if not biased:
+        assert got_ids[3].tolist() == list(range(top_k))
+    unscaled = torch.empty_like(weights)
+    ops().router_topk(dev(logits), dev(bias) if biased else None, top_k, False, 2.5, ids, unscaled)
+    close(f64(unscaled), 2.5 * picked, 2e-6, "weights without renormalising, scaled")
+
+
+@pytest.mark.parametrize("tokens,top_k,experts", [(1, 8, 256), (64, 8, 256), (700, 3, 11), (3000, 2, 4), (5, 1, 1)])
+def test_expert_plan_lists_every_assignment_once(tokens, top_k, experts):
+    rng = np.random.default_rng(6)
+    ids = np.stack([rng.permutation(experts)[:top_k] for _ in range(tokens)]).astype(np.int32)
+    n = tokens * top_k
+    tile = 32
+    max_tiles = (n + tile - 1) // tile + min(experts, n)
+    i32 = lambda k: torch.full((k,), -7, dtype=torch.int32, device=DEV)
+    counts, offsets, sorted_token, row_of = i32(((n + 1023) // 1024) * experts), i32(experts + 1), i32(n), i32(n)
+    tile_expert, tile_row0, num_tiles = i32(max_tiles), i32(max_tiles), i32(1)
+    ops().expert_plan(dev(ids), experts, tile, counts, offsets, sorted_token, row_of, tile_expert, tile_row0, num_tiles)
+    off, st, ro = offsets.cpu().numpy(), sorted_token.cpu().numpy(), row_of.cpu().numpy()
+    count = np.bincount(ids.reshape(-1), minlength=experts)
+    np.testing.assert_array_equal(off, np.concatenate([[0], np.cumsum(count)]))
+    assert sorted(ro.tolist()) == list(range(n))                                # a permutation
+    flat = ids.reshape(-1)
+    for a in range(n):
+        e = flat[a]
+        assert off[e] <= ro[a] < off[e + 1] and st[ro[a]] == a // top_k
+    for e in range(experts):                                                    # stable within an expert
+        rows = ro[flat == e]
+        assert (np.diff(rows) > 0).all()
+    nt = int(num_tiles.item())
+    te, tr = tile_expert.cpu().numpy()[:nt], tile_row0.cpu().numpy()[:nt]
+    want = [(e, off[e] + r) for e in range(experts) for r in range(0, count[e], tile)]
+    assert list(zip(te.tolist(), tr.tolist())) == want and nt <= max_tiles
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("experts,width,hidden,rows_per", [(4, 48, 96, [0, 1, 33, 70]), (3, 1536, 256, [5, 0, 64]),
+                                                           (7, 50, 70, [1, 1, 1, 1, 40, 0, 2])])
+def test_expert_products(dtype, experts, width, hidden, rows_per):
+    rng = np.random.default_rng(7)
+    w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.1, TORCH[dtype])
+    w2 = dev(rng.normal(size=(experts, hidden, width)) * 0.1, TORCH[dtype])
+    tokens = 90
+    x = dev(rng.normal(size=(tokens, hidden)), TORCH[dtype])
+    n = sum(rows_per)
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    sorted_token = rng.integers(0, tokens, size=n).astype(np.int32)
+    tiles = [(e, offsets[e] + r) for e in range(experts) for r in range(0, rows_per[e], 32)]
+    tile_expert = np.array([t[0] for t in tiles] + [0, 0], dtype=np.int32)
+    tile_row0 = np.array([t[1] for t in tiles] + [0, 0], dtype=np.int32)
+    num_tiles = np.array([len(tiles)], dtype=np.int32)
+    hidden_out = torch.full((n, width), 9.0, dtype=TORCH[dtype], device=DEV)
+    ops().expert_gemm_generic(w13, x, dev(sorted_token), dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                              len(tiles) + 2, hidden_out, paired=True)
+    xs, w13f, w2f = f64(x), f64(w13), f64(w2)
+    expert_of = np.repeat(np.arange(experts), rows_per)
+    ref_h = np.stack([pm.silu(xs[sorted_token[r]] @ w13f[expert_of[r], :width].T) * (xs[sorted_token[r]] @ w13f[expert_of[r], width:].T)
+                      for r in range(n)])
+    close(f64(hidden_out), ref_h, TOL[dtype], "gate/up product")
+    y = torch.full((n, hidden), 9.0, dtype=torch.float32, device=DEV)
+    ops().expert_gemm_generic(w2, hidden_out, None, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                              len(tiles) + 2, y, paired=False)
+    ref_y = np.stack([f64(hidden_out)[r] @ w2f[expert_of[r]].T for r in range(n)])
+    close(f64(y), ref_y, 3e-6 if dtype == "float32" else 2e-5, "down product")
+
+
+def test_combine_in_rank_order():
+    rng = np.random.default_rng(8)
+    tokens, top_k, width = 13, 3, 70
+    y = rng.normal(size=(tokens * top_k, width)).astype(np.float32)
+    w = rng.random(size=(tokens, top_k)).astype(np.float32)
+    row_of = rng.permutation(tokens * top_k).astype(np.int32)
+    out = torch.empty(tokens, width, dtype=torch.float32, device=DEV)
+    ops().expert_combine(dev(y), dev(w), dev(row_of), out)
+    ref = np.zeros((tokens, width), dtype=np.float32)
+    for t in range(tokens):
+        for r in range(top_k):
+            ref[t] = ref[t] + w[t, r] * y[row_of[t * top_k + r]]
+    close(f64(out), ref, 1e-6, "combine")
+
+
+def test_gated_unit():
+    rng = np.random.default_rng(9)
+    both = rng.normal(size=(7, 2 * 33)).astype(np.float32)
+    out = torch.empty(7, 33, dtype=torch.bfloat16, device=DEV)
+    ops().gated_unit(dev(both), out)
+    close(f64(out), pm.silu(both[:, :33].astype(np.float64)) * both[:, 33:], 5e-3, "gated unit")
+
+
+@pytest.mark.parametrize("vocab", [131, 4096, 200064])
+def test_picking_tokens(vocab):
+    rng = np.random.default_rng(10)
+    rows = 12
+    logits = (3 * rng.normal(size=(rows, vocab))).astype(np.float32)
+    logits[1, [5, vocab - 2]] = logits[1].max() + 1.0                      # a tie: the last index wins
+    logits[2, 0] = logits[2].max() + 2.0
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample_rows(dev(logits), None, None, out)
+    assert out.tolist() == [pm.greedy_pick(r) for r in logits] and out[1].item() == vocab - 2
+    temperature = np.array([0.0, 0.7, 1.0, 1.3, 0.2, 2.0, 0.9, 1.0, 0.5, 1.1, 1.0, 3.0], dtype=np.float32)
+    uniform = rng.random(size=rows).astype(np.float32)
+    uniform[2], uniform[3] = 0.0, 0.99999994
+    ops().sample_rows(dev(logits), dev(temperature), dev(uniform), out)
+    got = out.tolist()
+    assert got[0] == pm.greedy_pick(logits[0])
+    for r in range(1, rows):
+        want = pm.temperature_pick(logits[r], temperature[r], uniform[r])
+        if got[r] != want:                                                # float32 cumulative sums may differ by one place
+            p = np.exp((logits[r].astype(np.float64) - logits[r].max()) / temperature[r])
+            c = np.cumsum(p) / p.sum()
+            assert abs(c[got[r]] - uniform[r]) < 1e-5 or abs(c[max(got[r] - 1, 0)] - uniform[r]) < 1e-5, (r, got[r], want)
+    counts = np.zeros(4)
+    few = np.tile(np.log(np.array([0.1, 0.2, 0.3, 0.4], dtype=np.float32)), (4000, 1))
+    picks = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops().sample_rows(dev(few), dev(np.ones(4000, dtype=np.float32)), dev(rng.random(size=4000).astype(np.float32)), picks)
+    for v in picks.tolist():
+        counts[v] += 1
+    assert np.abs(counts / 4000 - np.array([0.1, 0.2, 0.3, 0.4])).max() < 0.03

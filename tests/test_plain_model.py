@@ -55,7 +55,7 @@ def test_attention_is_causal_grouped_and_windowed():
     np.testing.assert_allclose(out[:5], pm.causal_attention(q[:5], k[:5], v[:5], nh, nkv, hd, hd ** -0.5))
     for h in range(nh):                                          # row 0 sees key 0 only
         np.testing.assert_allclose(out[0, h * hd:(h + 1) * hd], v[0, (h // 2) * hd:(h // 2 + 1) * hd])
-    k2 = k.copy(); k2[:, :hd] += 1.0                             # kv head 0 feeds query heads 0 and 1 only
+    k2 = k.copy(); k2[:, :hd] += rng.normal(size=(T, hd))                            # kv head 0 feeds query heads 0 and 1 only
     out2 = pm.causal_attention(q, k2, v, nh, nkv, hd, hd ** -0.5)
     assert not np.allclose(out2[:, :2 * hd], out[:, :2 * hd]) and np.allclose(out2[:, 2 * hd:], out[:, 2 * hd:])
     win = pm.causal_attention(q, k, v, nh, nkv, hd, hd ** -0.5, window=3)
