@@ -1,0 +1,297 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of fieldrun_b200 at MiniMax-M2 layer sizes, random weights, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+
+Prints one JSON line.  A step is one decode step of a batch of --batch sequences (default 8) whose
+prompts of 2,048 tokens were run first; `value` is decoded tokens a second with the tokens staying on the
+device, `e2e` the same through the Python entry point with host tokens in and out every step.  It also
+times a prefill of one 2,048-token prompt and decode steps at batch 1 and 64.  With --gpus above 1 it
+says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference
+cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# MiniMax-M2 layer sizes, 16 layers: the configuration the headline numbers are quoted on
+M2 = dict(
+    architectures=["MiniMaxM2ForCausalLM"], model_type="minimax_m2", hidden_size=3072, num_attention_heads=48,
+    num_key_value_heads=8, head_dim=128, rotary_dim=64, rope_theta=5000000.0, use_qk_norm=True, num_local_experts=256,
+    num_experts_per_tok=8, intermediate_size=1536, vocab_size=200064, rms_norm_eps=1e-6, tie_word_embeddings=False)
+FULL_LAYERS = 16
+PROMPT = 2048
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                data = json.load(handle)
+            out = dict(FALLBACK_PEAKS)
+            for key in out:
+                if isinstance(data.get(key), (int, float)):
+                    out[key] = float(data[key])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", default="fieldrun_b200")
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--skip-points", action="store_true", help="leave out prefill and the batch 1/64 points")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust program; this image has no "
+                          "cargo/rustc and no network for its crates, so it cannot be built or installed offline"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(f"bench.py: fieldrun_b200 is a single-GPU library; --gpus {args.gpus} is not supported (run with --gpus 1)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    import fieldrun_b200 as fr
+    from fieldrun_b200.csrc import ops
+    from fieldrun_b200.engine.context import StepContext
+
+    torch.cuda.set_device(0)
+    peak, peak_source = peaks()
+    config = dict(M2, num_hidden_layers=args.layers)
+    largest = max(args.batch, 1 if args.skip_points else 64)
+    max_tokens = largest * CONTEXT + 2 * CONTEXT
+    t0 = time.time()
+    lm = fr.random_model(config, fr.RandomInit(seed=2, matrix_std=0.02, norm_std=0.1, bias_std=0.01), dtype="bfloat16",
+                         max_tokens=max_tokens, num_slots=largest + 2, max_batch=largest)
+    engine = lm.engine
+    model = lm.model
+    cfg = lm.config
+    load_s = time.time() - t0
+    rng = np.random.default_rng(0)
+
+    def prompts(n, length):
+        return [rng.integers(0, cfg.vocab_size, size=length).tolist() for _ in range(n)]
+
+    def fill(batch, real):
+        """Sequences holding PROMPT tokens each: by running the prompts, or (for the side points) by
+        reserving the pages and filling them with random keys and values."""
+        slots = [engine.new_sequence() for _ in range(batch)]
+        if real:
+            logits = engine.step(slots, prompts(batch, PROMPT))
+        else:
+            engine.cache.begin_step(slots, [PROMPT] * batch)
+            engine.cache.end_step(slots, [PROMPT] * batch)
+            for group in engine.cache.groups:
+                for t in (group.keys, group.values):
+                    t.normal_()
+            logits = torch.randn(batch, cfg.vocab_size, device="cuda")
+        first = torch.empty(batch, dtype=torch.int32, device="cuda")
+        ops.sample_rows(logits.contiguous(), None, None, first)
+        return slots, first
+
+    def device_step(slots, tokens_dev):
+        """One decode step whose tokens come from and go to the device."""
+        starts = [engine.cache.length(s) for s in slots]
+        ones = [1] * len(slots)
+        engine.cache.begin_step(slots, ones)
+        ctx = StepContext(engine.workspace, model.dtype, slots, starts, ones)
+        rows = torch.arange(len(slots), dtype=torch.int32, device="cuda")
+        logits = model.forward(ctx, engine.cache, tokens_dev, rows)
+        engine.cache.end_step(slots, ones)
+        out = torch.empty(len(slots), dtype=torch.int32, device="cuda")
+        ops.sample_rows(logits, None, None, out)
+        return out
+
+    def time_decode(slots, first, steps, warmup):
+        tokens = first
+        for _ in range(warmup):
+            tokens = device_step(slots, tokens)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = ops.launches()
+        start.record()
+        for _ in range(steps):
+            tokens = device_step(slots, tokens)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps, ops.launches() - before, tokens
+
+    def decode_bytes(slots):
+        """Bytes one decode step has to read: every weight it uses once (the experts actually picked, per
+        layer) and the keys and values of the live sequences."""
+        picked: list[int] = []
+        for block in model.blocks:
+            block.feed_forward.on_route = lambda ids: picked.append(int(torch.unique(ids).numel()))
+        probe = torch.randint(0, cfg.vocab_size, (len(slots),), dtype=torch.int32, device="cuda")
+        device_step(slots, probe)
+        torch.cuda.synchronize()
+        for block in model.blocks:
+            block.feed_forward.on_route = None
+        d, hd = cfg.hidden_size, cfg.head_dim
+        attn = ((cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * hd * d + cfg.num_attention_heads * hd * d) * 2
+        router = cfg.num_local_experts * d * 4
+        expert = 3 * cfg.intermediate_size * d * 2
+        weights = sum(attn + router + n * expert for n in picked) + cfg.vocab_size * d * 2
+        kv = sum(engine.cache.length(s) for s in slots) * 2 * cfg.num_key_value_heads * hd * 2 * len(model.blocks)
+        return weights + kv, picked
+
+    result: dict = {}
+    sampler = ClockSampler()
+
+    # ---- the headline: decode at --batch ------------------------------------------------------------------
+    slots, first = fill(args.batch, real=True)
+    sampler.start()
+    ms_step, launches, tokens = time_decode(slots, first, args.steps, args.warmup)
+    clocks = sampler.stop()
+    value = args.batch * 1000.0 / ms_step
+    step_bytes, picked = decode_bytes(slots)
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: host tokens in and out through Engine.step / Engine.pick ---------------------------------
+    host_tokens = tokens.tolist()
+    pinned_in = torch.empty(args.batch, dtype=torch.int32).pin_memory()
+    for _ in range(args.warmup):
+        host_tokens = engine.pick(engine.step(slots, [[t] for t in host_tokens]))
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    for _ in range(args.steps):
+        pinned_in.copy_(torch.tensor(host_tokens, dtype=torch.int32))
+        host_tokens = engine.pick(engine.step(slots, [[t] for t in pinned_in.tolist()]))
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - begin) * 1000.0 / args.steps
+    for s in slots:
+        engine.release(s)
+
+    result.update({
+        "metric": "MiniMax-M2 decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens", "value": round(value, 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random weights", "impl": "fieldrun_b200",
+        "config": {
+            "model": "MiniMax-M2 layer sizes", "layers": args.layers, "layers_of_config": FULL_LAYERS,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "rotary_dim": cfg.rotary_dim, "experts": cfg.num_local_experts,
+            "top_k": cfg.num_experts_per_tok, "expert_width": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
+            "l2": "weights read per step exceed L2", "peaks": peak_source,
+        },
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": 4 * args.batch + 4 * (7 * args.batch + 1), "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "bytes_per_step": step_bytes,
+                     "experts_per_layer": round(sum(picked) / max(len(picked), 1), 1), "of": peak_source},
+        "load_s": round(load_s, 1),
+    })
+
+    if not args.skip_points:
+        # ---- prefill of one 2,048-token prompt -------------------------------------------------------------
+        for attempt in range(2):                                    # the first run warms up
+            slot = engine.new_sequence()
+            ids = prompts(1, PROMPT)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step([slot], ids)
+            stop.record()
+            torch.cuda.synchronize()
+            prefill_ms = start.elapsed_time(stop)
+            engine.release(slot)
+        d, hd, nh, nkv = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+        per_layer = (2 * PROMPT * d * (nh + 2 * nkv) * hd + 4 * nh * hd * PROMPT * (PROMPT + 1) // 2 + 2 * PROMPT * nh * hd * d
+                     + 2 * PROMPT * d * cfg.num_local_experts + 2 * PROMPT * cfg.num_experts_per_tok * 3 * cfg.intermediate_size * d)
+        flops = per_layer * args.layers + 2 * d * cfg.vocab_size
+        result["prefill"] = {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                             "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "flops": flops}
+        # ---- decode at batch 1 and 64 ------------------------------------------------------------------------
+        points = {}
+        for batch in (1, 64):
+            slots, first = fill(batch, real=False)
+            ms, _, _ = time_decode(slots, first, max(8, args.steps // 2), 3)
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 2)
+            for s in slots:
+                engine.release(s)
+        points[f"decode_b{args.batch}"] = round(value, 2)
+        result["points"] = points
+
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

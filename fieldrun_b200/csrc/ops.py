@@ -92,9 +92,20 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_LAUNCHES = 0
+_KERNELS_PER_CALL = {"frb_expert_plan": 3}
+
+
+def launches() -> int:
+    """How many kernels of this library have been launched by this process."""
+    return _LAUNCHES
+
+
 def _call(name: str, *args) -> None:
+    global _LAUNCHES
     lib = library()
     status = getattr(lib, name)(*args, _stream())
+    _LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
     if status != 0:
         raise KernelError(f"{name}: {lib.frb_last_error().decode(errors='replace')} (status {status})")
 

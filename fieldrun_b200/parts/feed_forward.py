@@ -44,6 +44,7 @@ class RoutedExperts(FeedForward):
         self.bias: Optional[torch.Tensor] = None
         self.w13: Optional[torch.Tensor] = None
         self.w2: Optional[torch.Tensor] = None
+        self.on_route = None              # called with the picked ids [T, k] of every step (for measurements)
 
     def _expert_needs(self, e: int) -> tuple[TensorNeed, TensorNeed, TensorNeed]:
         d, i = self.hidden_size, self.expert_width
@@ -116,6 +117,8 @@ class RoutedExperts(FeedForward):
         if act32 is None:
             raise ValueError("routed experts need the normed rows in float32 for the router")
         ids, weights = self.route(ctx, act32)
+        if self.on_route is not None:
+            self.on_route(ids)
         p = self.plan(ctx, ids)
         y = self.experts(ctx, act, p)
         out = ctx.buffer("experts.out", (act.shape[0], self.hidden_size), torch.float32)
