@@ -51,7 +51,7 @@ class LineView:
     """What a mixer sees of its cache line."""
 
     keys: torch.Tensor | None            # [num_pages, kv_heads, PAGE_TOKENS, head_dim]
-    values: torch.Tensor | None
+    values: torch.Tensor | None          # [num_pages, kv_heads, head_dim, PAGE_TOKENS]
     page_table: torch.Tensor | None      # int32 [num_slots, max_pages]; -1 where no page is held
     window: int | None
     state: torch.Tensor | None           # float32 [num_slots, *state_shape]
@@ -70,7 +70,9 @@ class _Group:
         shape = (len(self.lines), num_pages, self.kv_heads, PAGE_TOKENS, self.head_dim)
         if allocate:
             self.keys = torch.zeros(shape, dtype=dtype, device=device)
-            self.values = torch.zeros(shape, dtype=dtype, device=device)
+            # within a page the values lie transposed, [head_dim, PAGE_TOKENS]: the product P @ V then reads
+            # runs of neighbouring keys
+            self.values = torch.zeros(shape[:3] + (self.head_dim, PAGE_TOKENS), dtype=dtype, device=device)
             self.table_dev = torch.full((num_slots, num_pages), -1, dtype=torch.int32, device=device)
         else:
             self.keys = self.values = self.table_dev = None

@@ -11,7 +11,7 @@
 struct AttnParams {
     const void* q;            // [T, nh, hd]
     const void* k_pages;      // [pages, nkv, PAGE, hd]
-    const void* v_pages;
+    const void* v_pages;      // [pages, nkv, hd, PAGE]: values lie transposed within a page
     const int* page_table;    // [slots, max_pages]
     const int* tok_pos;       // [T]
     const int* tok_slot;      // [T]
@@ -57,12 +57,17 @@ __global__ void attention_generic_kernel(AttnParams p) {
         for (int j0 = (lo / KEY_BLOCK) * KEY_BLOCK; j0 <= hi; j0 += KEY_BLOCK) {
             __syncthreads();
             const int page = table[j0 / FRB_PAGE];
-            const size_t base = (((size_t)page * p.num_kv_heads + g) * FRB_PAGE + (j0 % FRB_PAGE)) * hd;
+            const size_t head_base = ((size_t)page * p.num_kv_heads + g) * FRB_PAGE * hd;
+            const int in_page = j0 % FRB_PAGE;
             for (int i = threadIdx.x; i < KEY_BLOCK * hd; i += blockDim.x) {
                 const int r = i / hd, d = i - r * hd;
                 const bool valid = (j0 + r >= lo) && (j0 + r <= hi);
-                k_tile[r * (hd + 1) + d] = valid ? to_f32<T>(k_pages[base + i]) : 0.f;
-                v_tile[r * hd + d] = valid ? to_f32<T>(v_pages[base + i]) : 0.f;
+                k_tile[r * (hd + 1) + d] = valid ? to_f32<T>(k_pages[head_base + (size_t)(in_page + r) * hd + d]) : 0.f;
+            }
+            for (int i = threadIdx.x; i < KEY_BLOCK * hd; i += blockDim.x) {
+                const int d = i / KEY_BLOCK, r = i - d * KEY_BLOCK;          // keys of one dim are neighbours in memory
+                const bool valid = (j0 + r >= lo) && (j0 + r <= hi);
+                v_tile[r * hd + d] = valid ? to_f32<T>(v_pages[head_base + (size_t)d * FRB_PAGE + in_page + r]) : 0.f;
             }
             __syncthreads();
             if (active) {

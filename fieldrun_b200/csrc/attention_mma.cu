@@ -1,0 +1,339 @@
+// Tensor-core attention over the paged cache for bfloat16 models: one kernel for steps in which every
+// sequence brings one token (keys split over blocks, partial results merged in a fixed order) and one for
+// steps that bring many tokens per sequence (causal, blockwise with an online softmax).
+//
+// The formula is the reference's (src/minimax.rs:270-281): s = q.k * scale over the visible keys,
+// p = softmax(s), out = p V, query head h reading kv head h / (heads / kv_heads).  Scores, the running
+// maximum and sum, and both accumulators are float32; only the operands of the two products are bfloat16.
+//
+// Both kernels work on tiles of 16 rows x 64 keys (one cache page) held in registers.  Operands go from
+// global memory straight into mma.sync fragments with 16-byte loads: a product over k does not depend on
+// the order of k, so each thread takes 8 neighbouring elements of k for two MMAs instead of the scattered
+// pairs of the fragment layout, on both operands alike.  Values lie transposed within a page
+// ([head_dim][64 keys]), which makes the keys of P @ V neighbours in memory too.
+#include "common.cuh"
+
+#define ATT_CHUNK 256          // keys per block of the one-token kernel: 4 warps x 1 page
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile of 16 rows: lane = 4 g + t holds rows g and g + 8.
+template <int HD>
+struct RowTile {
+    uint4 q[HD / 32][2];       // [32 dims][row g | row g+8]: dims 32 s + 8 t .. + 7
+    float o[HD / 8][4];        // [8 dims]: (row g, dims 8 n + 2t, +1), (row g+8, same dims)
+    float m[2], l[2];          // running maximum (in units of log2) and sum of rows g and g + 8
+};
+
+template <int HD>
+__device__ __forceinline__ void tile_init(RowTile<HD>& st) {
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st.o[n][e] = 0.f;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+}
+
+// Adds one page of 64 keys to the tile.  k_page: [64][HD]; vt_page: [HD][64]; key_base: position of the
+// page's first key; row r sees keys lo[r] <= j <= hi[r].  scale2 = softmax scale * log2(e).
+template <int HD>
+__device__ __forceinline__ void tile_page(RowTile<HD>& st, const bf16* __restrict__ k_page, const bf16* __restrict__ vt_page,
+                                          int key_base, const int (&lo)[2], const int (&hi)[2], float scale2, int g, int t) {
+    float s[8][4];
+    // scores: column block 4 m + u, column c = 2 t' + d of it stands for key 32 m + 8 t' + 2 u + d
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int key_local = 32 * m + 8 * (g >> 1) + 2 * u + (g & 1);
+            const uint4* kp = reinterpret_cast<const uint4*>(k_page + (size_t)key_local * HD) + t;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int step = 0; step < HD / 32; ++step) {
+                const uint4 kb = __ldg(kp + step * 4);
+                mma_bf16(acc, st.q[step][0].x, st.q[step][1].x, st.q[step][0].y, st.q[step][1].y, kb.x, kb.y);
+                mma_bf16(acc, st.q[step][0].z, st.q[step][1].z, st.q[step][0].w, st.q[step][1].w, kb.z, kb.w);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[4 * m + u][e] = acc[e];
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
+                const float v = (key >= lo[r] && key <= hi[r]) ? s[4 * m + u][e] * scale2 : -INFINITY;
+                s[4 * m + u][e] = v;
+                mx[r] = fmaxf(mx[r], v);
+            }
+    float corr[2], sum[2] = {0.f, 0.f}, m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(st.m[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
+        corr[r] = exp2f(st.m[r] - m_use[r]);
+        st.m[r] = m_new;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pv = exp2f(s[j][e] - m_use[e >> 1]);
+            s[j][e] = pv;
+            sum[e >> 1] += pv;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        st.l[r] = st.l[r] * corr[r] + sum[r];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
+        st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
+    }
+    // out += P V: the thread's 8 keys 32 m + 8 t .. + 7 are one 16-byte run of a transposed value row
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        const uint32_t a0 = pack_bf16(s[4 * m][0], s[4 * m][1]), a1 = pack_bf16(s[4 * m][2], s[4 * m][3]);
+        const uint32_t a2 = pack_bf16(s[4 * m + 1][0], s[4 * m + 1][1]), a3 = pack_bf16(s[4 * m + 1][2], s[4 * m + 1][3]);
+        const uint32_t b0 = pack_bf16(s[4 * m + 2][0], s[4 * m + 2][1]), b1 = pack_bf16(s[4 * m + 2][2], s[4 * m + 2][3]);
+        const uint32_t b2 = pack_bf16(s[4 * m + 3][0], s[4 * m + 3][1]), b3 = pack_bf16(s[4 * m + 3][2], s[4 * m + 3][3]);
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            const uint4 vb = __ldg(reinterpret_cast<const uint4*>(vt_page + (size_t)(8 * n + g) * FRB_PAGE + 32 * m) + t);
+            mma_bf16(st.o[n], a0, a1, a2, a3, vb.x, vb.y);
+            mma_bf16(st.o[n], b0, b1, b2, b3, vb.z, vb.w);
+        }
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void load_q_row(RowTile<HD>& st, int half, const bf16* __restrict__ row, int t) {
+#pragma unroll
+    for (int step = 0; step < HD / 32; ++step)
+        st.q[step][half] = row ? __ldg(reinterpret_cast<const uint4*>(row + 32 * step) + t) : make_uint4(0, 0, 0, 0);
+}
+
+// ----------------------------------------------------------------------------- one token per sequence
+
+struct DecodeAttnParams {
+    const bf16* q;             // [B, nh, HD]
+    const bf16* k_pages;       // [pages, nkv, 64, HD]
+    const bf16* v_pages;       // [pages, nkv, HD, 64]
+    const int* page_table;     // [slots, max_pages]
+    const int* seq_pos;        // [B] position of the sequence's token
+    const int* seq_slot;       // [B]
+    float* part_o;             // [B, nh, max_chunks, HD]
+    float* part_ml;            // [B, nh, max_chunks, 2]
+    bf16* out;                 // [B, nh * HD]
+    float scale2;
+    int window, max_pages, num_heads, num_kv_heads, max_chunks;
+};
+
+// grid (chunk, kv head, sequence), 4 warps.  Rows of the tile are the query heads of the kv head's group.
+template <int HD>
+__global__ void __launch_bounds__(128) attention_decode_mma_kernel(DecodeAttnParams p) {
+    __shared__ float sm_o[4][16][HD + 4];
+    __shared__ float sm_m[4][16], sm_l[4][16];
+    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int group = p.num_heads / p.num_kv_heads;
+    const int pos = p.seq_pos[b];
+    const int hi_key = pos, lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (chunk * ATT_CHUNK > hi_key || (chunk + 1) * ATT_CHUNK <= lo_key) return;      // the merge skips these chunks
+
+    RowTile<HD> st;
+    tile_init(st);
+    const int page_index = chunk * (ATT_CHUNK / FRB_PAGE) + warp;
+    const int key_base = page_index * FRB_PAGE;
+    if (key_base <= hi_key && key_base + FRB_PAGE > lo_key) {
+        const bf16* q_base = p.q + ((size_t)b * p.num_heads + (size_t)kvh * group) * HD;
+        load_q_row(st, 0, g < group ? q_base + (size_t)g * HD : nullptr, t);
+        load_q_row(st, 1, g + 8 < group ? q_base + (size_t)(g + 8) * HD : nullptr, t);
+        const int page = p.page_table[(size_t)p.seq_slot[b] * p.max_pages + page_index];
+        const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
+        const int lo[2] = {lo_key, lo_key}, hi[2] = {hi_key, hi_key};
+        tile_page(st, p.k_pages + at, p.v_pages + at, key_base, lo, hi, p.scale2, g, t);
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        sm_o[warp][g][8 * n + 2 * t] = st.o[n][0];
+        sm_o[warp][g][8 * n + 2 * t + 1] = st.o[n][1];
+        sm_o[warp][g + 8][8 * n + 2 * t] = st.o[n][2];
+        sm_o[warp][g + 8][8 * n + 2 * t + 1] = st.o[n][3];
+    }
+    if (t == 0) {
+        sm_m[warp][g] = st.m[0]; sm_l[warp][g] = st.l[0];
+        sm_m[warp][g + 8] = st.m[1]; sm_l[warp][g + 8] = st.l[1];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += 128) {
+        const int r = idx / HD, d = idx - r * HD;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) top = fmaxf(top, sm_m[w][r]);
+        float sum = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(sm_m[w][r] - top);        // a warp without visible keys has m = -inf: f = 0
+            sum += sm_l[w][r] * f;
+            acc += sm_o[w][r][d] * f;
+        }
+        const size_t row = ((size_t)b * p.num_heads + (size_t)kvh * group + r) * p.max_chunks + chunk;
+        p.part_o[row * HD + d] = acc;
+        if (d == 0) { p.part_ml[row * 2] = top; p.part_ml[row * 2 + 1] = sum; }
+    }
+}
+
+// grid (head, sequence): merges the chunks of one (sequence, head), first chunk to last.
+template <int HD>
+__global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnParams p) {
+    const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int pos = p.seq_pos[b];
+    const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first = lo_key / ATT_CHUNK, last = pos / ATT_CHUNK;
+    const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
+    float top = -INFINITY;
+    for (int c = first; c <= last; ++c) top = fmaxf(top, p.part_ml[(row0 + c) * 2]);
+    float sum = 0.f, acc = 0.f;
+    for (int c = first; c <= last; ++c) {
+        const float f = exp2f(p.part_ml[(row0 + c) * 2] - top);
+        sum += p.part_ml[(row0 + c) * 2 + 1] * f;
+        acc += p.part_o[(row0 + c) * HD + d] * f;
+    }
+    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(acc / sum);
+}
+
+FRB_API int frb_attention_decode_mma(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
+                                     int max_pages, const int* seq_pos, const int* seq_slot, float* part_o, float* part_ml,
+                                     void* out, int num_seqs, int num_heads, int num_kv_heads, int head_dim, float scale,
+                                     int window, int max_chunks, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
+    FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
+                  "one-token attention: %d heads over %d kv heads (groups of at most 16)", num_heads, num_kv_heads);
+    FRB_CHECK_ARG(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
+                  "one-token attention: head_dim %d is not 32, 64, 96 or 128", head_dim);
+    FRB_CHECK_ARG(num_seqs <= 65535 && num_kv_heads <= 65535, "one-token attention: %d sequences exceed the grid", num_seqs);
+    DecodeAttnParams p;
+    p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
+    p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
+    p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks;
+    dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
+#define LAUNCH(HD)                                                                  \
+    attention_decode_mma_kernel<HD><<<grid, 128, 0, stream>>>(p);                   \
+    attention_decode_merge_kernel<HD><<<merge_grid, HD, 0, stream>>>(p)
+    if (head_dim == 32) { LAUNCH(32); } else if (head_dim == 64) { LAUNCH(64); } else if (head_dim == 96) { LAUNCH(96); } else { LAUNCH(128); }
+#undef LAUNCH
+    FRB_RETURN_LAUNCH("attention_decode_mma");
+}
+
+// ----------------------------------------------------------------------------- many tokens per sequence
+
+struct PrefillAttnParams {
+    const bf16* q;             // [T, nh, HD]
+    const bf16* k_pages;
+    const bf16* v_pages;
+    const int* page_table;
+    const int* tile_seq;       // [tiles] sequence of the tile
+    const int* tile_q0;        // [tiles] first row of the tile among its sequence's new tokens
+    const int* seq_slot;       // [B]
+    const int* seq_start;      // [B] position of the sequence's first new token
+    const int* seq_q_len;      // [B]
+    const int* cu_q_len;       // [B + 1]
+    bf16* out;                 // [T, nh * HD]
+    float scale2;
+    int window, max_pages, num_heads, num_kv_heads;
+};
+
+// grid (tile of 16 queries, kv head); warps take the query heads of the group in turn, so the warps of a
+// block read the same keys and values at about the same time.
+template <int HD>
+__global__ void __launch_bounds__(256) attention_prefill_mma_kernel(PrefillAttnParams p) {
+    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
+    const int group = p.num_heads / p.num_kv_heads;
+    const int b = p.tile_seq[tile], q0 = p.tile_q0[tile];
+    const int q_len = p.seq_q_len[b], start = p.seq_start[b], tok0 = p.cu_q_len[b] + q0;
+    const int* table = p.page_table + (size_t)p.seq_slot[b] * p.max_pages;
+    int lo[2], hi[2];
+    bool valid[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        valid[r] = q0 + row < q_len;
+        hi[r] = valid[r] ? start + q0 + row : -1;
+        lo[r] = (valid[r] && p.window > 0) ? max(0, hi[r] - p.window + 1) : 0;
+    }
+    const int last_key = start + min(q0 + 15, q_len - 1);
+    const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    for (int hl = warp; hl < group; hl += nwarps) {
+        const int head = kvh * group + hl;
+        RowTile<HD> st;
+        tile_init(st);
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            load_q_row(st, r, valid[r] ? p.q + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD : nullptr, t);
+        for (int page_index = first_key / FRB_PAGE; page_index <= last_key / FRB_PAGE; ++page_index) {
+            const int page = table[page_index];
+            const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
+            tile_page(st, p.k_pages + at, p.v_pages + at, page_index * FRB_PAGE, lo, hi, p.scale2, g, t);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (!valid[r]) continue;
+            const float inv = 1.0f / st.l[r];
+            bf16* dst = p.out + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n)
+                *reinterpret_cast<uint32_t*>(dst + 8 * n + 2 * t) = pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+        }
+    }
+}
+
+FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
+                                      int max_pages, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                      const int* seq_slot, const int* seq_start, const int* seq_q_len, const int* cu_q_len,
+                                      void* out, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                      cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0, "attention: %d heads over %d kv heads", num_heads, num_kv_heads);
+    FRB_CHECK_ARG(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
+                  "attention: head_dim %d is not 32, 64, 96 or 128", head_dim);
+    FRB_CHECK_ARG(num_kv_heads <= 65535, "attention: %d kv heads exceed the grid", num_kv_heads);
+    PrefillAttnParams p;
+    p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start; p.seq_q_len = seq_q_len;
+    p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
+    p.max_pages = max_pages; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads;
+    const int group = num_heads / num_kv_heads;
+    const int nwarps = group < 8 ? group : 8;
+    dim3 grid(num_tiles, num_kv_heads);
+    if (head_dim == 32) attention_prefill_mma_kernel<32><<<grid, 32 * nwarps, 0, stream>>>(p);
+    else if (head_dim == 64) attention_prefill_mma_kernel<64><<<grid, 32 * nwarps, 0, stream>>>(p);
+    else if (head_dim == 96) attention_prefill_mma_kernel<96><<<grid, 32 * nwarps, 0, stream>>>(p);
+    else attention_prefill_mma_kernel<128><<<grid, 32 * nwarps, 0, stream>>>(p);
+    FRB_RETURN_LAUNCH("attention_prefill_mma");
+}

@@ -109,7 +109,7 @@ struct QkvParams {
     const int* page_table;    // [slots, max_pages]
     void* q_out;              // [T, nh, hd] OutT
     void* k_pages;            // [pages, nkv, PAGE, hd] OutT
-    void* v_pages;
+    void* v_pages;            // [pages, nkv, hd, PAGE] OutT: values lie transposed within a page
     float eps;
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
 };
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
         const InT* vsrc = src + q_width + k_width;
         for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
             const int head = i / hd, dim = i % hd;
-            const size_t at = (((size_t)page * p.num_kv_heads + head) * FRB_PAGE + in_page) * hd + dim;
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
             ((OutT*)p.v_pages)[at] = from_f32<OutT>(to_f32<InT>(vsrc[i]));
         }
     }

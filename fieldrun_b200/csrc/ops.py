@@ -31,6 +31,9 @@ _SIGNATURES = {
     "frb_expert_gemm_generic": "ppipppppipiiii",
     "frb_sample_rows": "piippp",
     "frb_gated_unit": "ppiii",
+    "frb_attention_decode_mma": "ppppipppppiiiifii",
+    "frb_attention_prefill_mma": "ppppippipppppiiifi",
+    "frb_expert_gemm_mma": "pppppppiipiii",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -93,7 +96,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_expert_plan": 3}
+_KERNELS_PER_CALL = {"frb_expert_plan": 3, "frb_attention_decode_mma": 2}
 
 
 def launches() -> int:
@@ -236,3 +239,44 @@ def gated_unit(both: torch.Tensor, out: torch.Tensor) -> None:
     _want(both, torch.float32, "gate and up rows")
     rows, width = out.shape
     _call("frb_gated_unit", _ptr(both), _ptr(out), _code(out.dtype), rows, width)
+
+
+MMA_HEAD_DIMS = (32, 64, 96, 128)
+ATTENTION_CHUNK = 256
+
+
+def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                         seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                         out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                         window: Optional[int], max_chunks: int) -> None:
+    """One token per sequence, bfloat16: keys split into chunks of 256 over blocks, merged in chunk order."""
+    for t in (q, k_pages, v_pages, out):
+        _want(t, torch.bfloat16, "tensor-core attention operands")
+    _want(part_o, torch.float32, "partial outputs")
+    _call("frb_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
+          _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads, num_kv_heads,
+          head_dim, float(scale), int(window or 0), max_chunks)
+
+
+def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                          tile_seq: torch.Tensor, tile_q0: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
+                          seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
+                          num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+    """Many tokens per sequence, bfloat16: tiles of 16 queries, causal, blockwise over the cache pages."""
+    for t in (q, k_pages, v_pages, out):
+        _want(t, torch.bfloat16, "tensor-core attention operands")
+    _call("frb_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
+          _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_q_len),
+          _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0))
+
+
+def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
+                    tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
+                    tile_rows: int, out: torch.Tensor, *, paired: bool) -> None:
+    """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows)."""
+    _want(w, torch.bfloat16, "streamed expert weights")
+    _want(x, torch.bfloat16, "streamed expert inputs")
+    _want(out, torch.bfloat16 if paired else torch.float32, "streamed expert outputs")
+    feats = w.shape[1] // 2 if paired else w.shape[1]
+    _call("frb_expert_gemm_mma", _ptr(w), _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired))

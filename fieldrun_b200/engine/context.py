@@ -75,5 +75,20 @@ class StepContext:
         self.seq_q_len = dev[o + 2 * b:o + 3 * b]
         self.cu_q_len = dev[o + 3 * b:o + 4 * b + 1]
 
+        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.buffer(name, shape, dtype)
+
+    def query_tiles(self, rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Tiles of ``rows`` consecutive new tokens that never span two sequences: (sequence of each tile,
+        first row of each tile among its sequence's new tokens), on the device."""
+        if rows not in self._tiles:
+            seqs, firsts = [], []
+            for b, n in enumerate(self.seq_q_lens):
+                for q0 in range(0, n, rows):
+                    seqs.append(b)
+                    firsts.append(q0)
+            both = torch.tensor([seqs, firsts], dtype=torch.int32).to(self.device)
+            self._tiles[rows] = (both[0].contiguous(), both[1].contiguous())
+        return self._tiles[rows]

@@ -102,6 +102,21 @@ class GQAAttention(Mixer):
         return linear(out, self.w_o)
 
     def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor) -> None:
+        """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128; the general kernel otherwise."""
+        common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                      scale=self.softmax_scale, window=self.window)
+        if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+            if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
+                chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
+                part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
+                part_ml = ctx.buffer("attention.part_ml", (ctx.num_seqs, self.num_heads, chunks, 2), torch.float32)
+                ops.attention_decode_mma(q, line.keys, line.values, line.page_table, ctx.seq_start, ctx.seq_slot, part_o,
+                                         part_ml, out, max_chunks=chunks, **common)
+            else:
+                tile_seq, tile_q0 = ctx.query_tiles(16)
+                ops.attention_prefill_mma(q, line.keys, line.values, line.page_table, tile_seq, tile_q0, ctx.seq_slot,
+                                          ctx.seq_start, ctx.seq_q_len, ctx.cu_q_len, out, **common)
+            return
         ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
                               num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                               scale=self.softmax_scale, window=self.window)

@@ -83,11 +83,24 @@ class RoutedExperts(FeedForward):
         ops.router_topk(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, ids, weights)
         return ids, weights
 
+    def streams(self) -> bool:
+        """Whether the tensor-core streaming kernel takes this part's sizes (bfloat16, sizes in steps of 32)."""
+        return (self.dtype == torch.bfloat16 and self.hidden_size % 32 == 0 and self.expert_width % 32 == 0)
+
+    def tile_rows(self, assignments: int) -> int:
+        """Rows of one expert that one block takes: few when experts get few rows each, so that no block
+        carries accumulators it does not need."""
+        if not self.streams():
+            return TILE_ROWS
+        per_expert = assignments / self.num_experts
+        return 8 if per_expert <= 4 else 16 if per_expert <= 12 else 32
+
     def plan(self, ctx, ids: torch.Tensor):
         tokens = ids.shape[0]
         n = tokens * self.top_k
         chunks = (n + 1023) // 1024
-        max_tiles = (n + TILE_ROWS - 1) // TILE_ROWS + min(self.num_experts, n)
+        tile_rows = self.tile_rows(n)
+        max_tiles = (n + tile_rows - 1) // tile_rows + min(self.num_experts, n)
         p = {
             "counts": ctx.buffer("experts.counts", (chunks * self.num_experts,), torch.int32),
             "offsets": ctx.buffer("experts.offsets", (self.num_experts + 1,), torch.int32),
@@ -98,17 +111,24 @@ class RoutedExperts(FeedForward):
             "num_tiles": ctx.buffer("experts.num_tiles", (1,), torch.int32),
             "max_tiles": max_tiles,
             "rows": n,
+            "tile_rows": tile_rows,
         }
-        ops.expert_plan(ids, self.num_experts, TILE_ROWS, p["counts"], p["offsets"], p["sorted_token"],
+        ops.expert_plan(ids, self.num_experts, tile_rows, p["counts"], p["offsets"], p["sorted_token"],
                         p["row_of_assign"], p["tile_expert"], p["tile_row0"], p["num_tiles"])
         return p
 
     def experts(self, ctx, act: torch.Tensor, p) -> torch.Tensor:
         """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order."""
         hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
+        y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
+        if self.streams():
+            ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
+                                p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True)
+            ops.expert_gemm_mma(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                                p["max_tiles"], p["tile_rows"], y, paired=False)
+            return y
         ops.expert_gemm_generic(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
                                 p["offsets"], p["max_tiles"], hidden, paired=True)
-        y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
         ops.expert_gemm_generic(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                 p["max_tiles"], y, paired=False)
         return y

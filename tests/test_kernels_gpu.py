@@ -82,7 +82,7 @@ def paged_cache(rng, slots, pages, kv_heads, head_dim, dtype):
     """A cache whose pages are handed out in a scrambled order, filled with junk where nothing was written."""
     order = rng.permutation(pages)
     keys = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)) * 5, TORCH[dtype])
-    values = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)) * 5, TORCH[dtype])
+    values = dev(rng.normal(size=(pages, kv_heads, head_dim, 64)) * 5, TORCH[dtype])
     table = np.full((slots, pages), -1, dtype=np.int32)
     return keys, values, table, list(order)
 
@@ -136,7 +136,7 @@ def test_qk_norm_rotary_and_cache_write(dtype, heads, kv_heads, head_dim, rotary
     for t in range(T):
         page = table[slot_of[t], positions[t] // 64]
         close(kc[page, :, positions[t] % 64, :].reshape(-1), k[t], TOL[dtype], f"key of token {t}")
-        close(vc[page, :, positions[t] % 64, :].reshape(-1), v[t], TOL[dtype], f"value of token {t}")
+        close(vc[page, :, :, positions[t] % 64].reshape(-1), v[t], TOL[dtype], f"value of token {t}")
 
 
 def reference_attention(q, kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window):
@@ -148,7 +148,7 @@ def reference_attention(q, kc, vc, table, positions, slot_of, heads, kv_heads, h
         for h in range(heads):
             g = h // rep
             k = np.stack([kc[table[slot, j // 64], g, j % 64] for j in js])
-            v = np.stack([vc[table[slot, j // 64], g, j % 64] for j in js])
+            v = np.stack([vc[table[slot, j // 64], g, :, j % 64] for j in js])
             s = (k @ q[t, h * head_dim:(h + 1) * head_dim]) * scale
             p = np.exp(s - s.max())
             out[t, h * head_dim:(h + 1) * head_dim] = (p / p.sum()) @ v
@@ -186,7 +186,7 @@ def test_attention_finds_one_far_key_and_respects_the_windows_edge(dtype):
     heads, kv_heads, head_dim, n = 4, 2, 32, 700
     pages = (n + 63) // 64
     keys = torch.zeros(pages, kv_heads, 64, head_dim, dtype=TORCH[dtype], device=DEV)
-    values = dev(rng.normal(size=(pages, kv_heads, 64, head_dim)), TORCH[dtype])
+    values = dev(rng.normal(size=(pages, kv_heads, head_dim, 64)), TORCH[dtype])
     table = np.arange(pages, dtype=np.int32)[::-1].copy()[None, :]
     far = 37
     page, row = table[0, far // 64], far % 64
@@ -196,14 +196,14 @@ def test_attention_finds_one_far_key_and_respects_the_windows_edge(dtype):
     out = torch.empty(1, heads * head_dim, dtype=TORCH[dtype], device=DEV)
     args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=1.0)
     ops().attention_generic(dev(q, TORCH[dtype]), keys, values, dev(table), dev(positions), dev(slot_of), out, window=None, **args)
-    want = np.repeat(f64(values)[page, :, row, :], heads // kv_heads, axis=0).reshape(1, -1)
+    want = np.repeat(f64(values)[page, :, :, row], heads // kv_heads, axis=0).reshape(1, -1)
     close(f64(out), want, 1e-5 if dtype == "float32" else 1e-2, "the far key")
     for window, inside in ((n - far, True), (n - far - 1, False)):
         ops().attention_generic(dev(q, TORCH[dtype]), keys, values, dev(table), dev(positions), dev(slot_of), out, window=window, **args)
         if inside:
             close(f64(out), want, 1e-5 if dtype == "float32" else 1e-2, "the far key at the window's edge")
         else:
-            mean = np.stack([f64(values)[table[0, j // 64], :, j % 64, :] for j in range(far + 1, n)]).mean(0)
+            mean = np.stack([f64(values)[table[0, j // 64], :, :, j % 64] for j in range(far + 1, n)]).mean(0)
             close(f64(out), np.repeat(mean, heads // kv_heads, axis=0).reshape(1, -1), 2e-5 if dtype == "float32" else 2e-2,
                   "one key past the window's edge")
 
@@ -348,3 +348,145 @@ def test_picking_tokens(vocab):
     for v in picks.tolist():
         counts[v] += 1
     assert np.abs(counts / 4000 - np.array([0.1, 0.2, 0.3, 0.4])).max() < 0.03
+
+
+# ----------------------------------------------------------------------------- tensor-core kernels (bfloat16)
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 1, 128, None), (8, 8, 64, None), (32, 2, 32, None),
+                                                            (12, 2, 96, 300), (48, 8, 128, 70)])
+def test_one_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window):
+    rng = np.random.default_rng(11)
+    lengths = {0: 1000, 1: 257, 2: 64, 4: 1, 5: 513}
+    keys, values, table, free = paged_cache(rng, 6, 32, kv_heads, head_dim, "bfloat16")
+    keys, values = keys * 0.2, values * 0.2
+    kc, vc = f64(keys), f64(values)
+    for slot, n in lengths.items():
+        for i in range((n + 63) // 64):
+            table[slot, i] = free.pop()
+    slot_of = np.array(list(lengths), dtype=np.int32)
+    positions = np.array([lengths[s] - 1 for s in slot_of], dtype=np.int32)
+    q = dev(rng.normal(size=(len(positions), heads * head_dim)), torch.bfloat16)
+    out = torch.full_like(q, 7.0)
+    chunks = (int(positions.max()) + 1 + 255) // 256
+    part_o = torch.full((len(positions), heads, chunks, head_dim), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((len(positions), heads, chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
+    scale = head_dim ** -0.5
+    ops().attention_decode_mma(q, keys, values, dev(table), dev(positions), dev(slot_of), part_o, part_ml, out,
+                               num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
+                               max_chunks=chunks)
+    ref = reference_attention(f64(q), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
+    close(f64(out), ref, 1e-2, "one-token attention")
+    general = torch.empty_like(q)
+    ops().attention_generic(q, keys, values, dev(table), dev(positions), dev(slot_of), general, num_heads=heads,
+                            num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+    close(f64(out), f64(general), 1e-2, "against the general kernel")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 1, 128, None), (4, 4, 64, None), (20, 2, 32, 40),
+                                                            (9, 3, 96, None)])
+def test_many_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window):
+    rng = np.random.default_rng(12)
+    # (slot, tokens already in the cache, new tokens)
+    seqs = [(0, 0, 100), (2, 130, 17), (3, 0, 1), (1, 63, 70), (5, 200, 16)]
+    keys, values, table, free = paged_cache(rng, 6, 24, kv_heads, head_dim, "bfloat16")
+    keys, values = keys * 0.2, values * 0.2
+    kc, vc = f64(keys), f64(values)
+    for slot, start, n in seqs:
+        for i in range((start + n + 63) // 64):
+            table[slot, i] = free.pop()
+    positions = np.concatenate([np.arange(start, start + n) for _, start, n in seqs]).astype(np.int32)
+    slot_of = np.concatenate([np.full(n, slot) for slot, _, n in seqs]).astype(np.int32)
+    q = dev(rng.normal(size=(len(positions), heads * head_dim)), torch.bfloat16)
+    out = torch.full_like(q, 7.0)
+    tile_seq = np.concatenate([np.full((n + 15) // 16, b) for b, (_, _, n) in enumerate(seqs)]).astype(np.int32)
+    tile_q0 = np.concatenate([np.arange(0, n, 16) for _, _, n in seqs]).astype(np.int32)
+    q_lens = np.array([n for _, _, n in seqs], dtype=np.int32)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    scale = head_dim ** -0.5
+    ops().attention_prefill_mma(q, keys, values, dev(table), dev(tile_seq), dev(tile_q0),
+                                dev(np.array([s for s, _, _ in seqs], dtype=np.int32)),
+                                dev(np.array([s for _, s, _ in seqs], dtype=np.int32)), dev(q_lens), dev(cu), out,
+                                num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+    ref = reference_attention(f64(q), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
+    close(f64(out), ref, 1e-2, "many-token attention")
+
+
+def test_tensor_core_attention_finds_one_far_key():
+    rng = np.random.default_rng(13)
+    heads, kv_heads, head_dim, n = 12, 2, 128, 900
+    pages = (n + 63) // 64
+    keys = torch.zeros(pages, kv_heads, 64, head_dim, dtype=torch.bfloat16, device=DEV)
+    values = dev(rng.normal(size=(pages, kv_heads, head_dim, 64)), torch.bfloat16)
+    table = np.arange(pages, dtype=np.int32)[::-1].copy()[None, :]
+    far = 70
+    page, row = table[0, far // 64], far % 64
+    keys[page, :, row, :] = 1.0
+    q = dev(np.full((1, heads * head_dim), 0.5), torch.bfloat16)
+    want = np.repeat(f64(values)[page, :, :, row], heads // kv_heads, axis=0).reshape(1, -1)
+    positions, slot_of = dev(np.array([n - 1], dtype=np.int32)), dev(np.array([0], dtype=np.int32))
+    chunks = (n + 255) // 256
+    part_o = torch.empty(1, heads, chunks, head_dim, dtype=torch.float32, device=DEV)
+    part_ml = torch.empty(1, heads, chunks, 2, dtype=torch.float32, device=DEV)
+    out = torch.empty_like(q)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=1.0)
+    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=None,
+                               max_chunks=chunks, **args)
+    close(f64(out), want, 1e-2, "far key, one token")
+    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far,
+                               max_chunks=chunks, **args)
+    close(f64(out), want, 1e-2, "far key at the window's edge")
+    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far - 1,
+                               max_chunks=chunks, **args)
+    mean = np.stack([f64(values)[table[0, j // 64], :, :, j % 64] for j in range(far + 1, n)]).mean(0)
+    close(f64(out), np.repeat(mean, heads // kv_heads, axis=0).reshape(1, -1), 2e-2, "one key past the window's edge")
+    one = dev(np.array([0], dtype=np.int32))
+    ops().attention_prefill_mma(q, keys, values, dev(table), one, one, one, positions, dev(np.array([1], dtype=np.int32)),
+                                dev(np.array([0, 1], dtype=np.int32)), out, window=None, **args)
+    close(f64(out), want, 1e-2, "far key, tile kernel")
+
+
+@pytest.mark.parametrize("tile_rows", [8, 16, 32])
+@pytest.mark.parametrize("experts,width,hidden,rows_per", [(4, 64, 96, [0, 1, 33, 70]), (3, 1536, 256, [5, 0, 9]),
+                                                           (6, 32, 3072, [1, 2, 8, 9, 0, 17])])
+def test_streamed_expert_products(tile_rows, experts, width, hidden, rows_per):
+    rng = np.random.default_rng(14)
+    w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.1, torch.bfloat16)
+    w2 = dev(rng.normal(size=(experts, hidden, width)) * 0.1, torch.bfloat16)
+    tokens = 50
+    x = dev(rng.normal(size=(tokens, hidden)), torch.bfloat16)
+    n = sum(rows_per)
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    sorted_token = rng.integers(0, tokens, size=n).astype(np.int32)
+    tiles = [(e, offsets[e] + r) for e in range(experts) for r in range(0, rows_per[e], tile_rows)]
+    tile_expert = np.array([t[0] for t in tiles] + [0, 0], dtype=np.int32)
+    tile_row0 = np.array([t[1] for t in tiles] + [0, 0], dtype=np.int32)
+    num_tiles = np.array([len(tiles)], dtype=np.int32)
+    hidden_out = torch.full((n, width), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops().expert_gemm_mma(w13, x, dev(sorted_token), dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                          len(tiles) + 2, tile_rows, hidden_out, paired=True)
+    xs, w13f, w2f = f64(x), f64(w13), f64(w2)
+    expert_of = np.repeat(np.arange(experts), rows_per)
+    ref_h = np.stack([pm.silu(xs[sorted_token[r]] @ w13f[expert_of[r], :width].T) * (xs[sorted_token[r]] @ w13f[expert_of[r], width:].T)
+                      for r in range(n)])
+    close(f64(hidden_out), ref_h, 1e-2, "streamed gate/up product")
+    y = torch.full((n, hidden), 9.0, dtype=torch.float32, device=DEV)
+    ops().expert_gemm_mma(w2, hidden_out, None, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                          len(tiles) + 2, tile_rows, y, paired=False)
+    ref_y = np.stack([f64(hidden_out)[r] @ w2f[expert_of[r]].T for r in range(n)])
+    close(f64(y), ref_y, 2e-5, "streamed down product")
+
+
+def test_kernels_refuse_sizes_they_do_not_take():
+    from fieldrun_b200.csrc.ops import KernelError
+    i32 = lambda *v: dev(np.array(v, dtype=np.int32))
+    w = torch.zeros(1, 16, 40, dtype=torch.bfloat16, device=DEV)
+    x = torch.zeros(4, 40, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="multiple of 32"):
+        ops().expert_gemm_mma(w, x, None, i32(0), i32(0), i32(1), i32(0, 4), 1, 8, torch.zeros(4, 16, device=DEV), paired=False)
+    q = torch.zeros(1, 2 * 48, dtype=torch.bfloat16, device=DEV)
+    kv = torch.zeros(1, 1, 64, 48, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="head_dim 48"):
+        ops().attention_decode_mma(q, kv, kv, i32(0).view(1, 1), i32(0), i32(0), torch.zeros(1, device=DEV), torch.zeros(1, device=DEV),
+                                   torch.zeros_like(q), num_heads=2, num_kv_heads=1, head_dim=48, scale=1.0, window=None, max_chunks=1)
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops().embed_rows(torch.zeros(1, dtype=torch.int32), torch.zeros(2, 2), torch.zeros(1, 2))
