@@ -51,19 +51,20 @@ def peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi; `window` reports the samples of a time span."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
         self.proc = None
-        self.lines: list[str] = []
+        self.samples: list[tuple[float, float, float, list[str]]] = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -71,39 +72,39 @@ class ClockSampler:
     def _read(self):
         assert self.proc is not None and self.proc.stdout is not None
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
             try:
-                clocks.append(float(parts[0]))
-                max_clock = float(parts[1])
+                clock, top = float(parts[0]), float(parts[1])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+            active = [n for n, flag in zip(self.NAMES, parts[2:6]) if flag.lower().startswith("active")]
+            self.samples.append((time.time(), clock, top, active))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def window(self, begin: float, end: float) -> dict:
+        if self.proc is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi gave no sample"], "samples": 0}
+        inside = [s for s in self.samples if begin <= s[0] <= end]
+        if not inside:                                   # a region shorter than the sampling period: the nearest sample
+            inside = [min(self.samples, key=lambda s: min(abs(s[0] - begin), abs(s[0] - end)))]
+        clocks = sorted(s[1] for s in inside)
+        reasons = sorted({r for s in inside for r in s[3]})
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": inside[0][2], "reasons": reasons, "samples": len(inside)}
 
 
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", default="fieldrun_b200")
     parser.add_argument("--layers", type=int, default=FULL_LAYERS)
@@ -127,9 +128,10 @@ def main() -> int:
 
     import fieldrun_b200 as fr
     from fieldrun_b200.csrc import ops
-    from fieldrun_b200.engine.context import StepContext
 
     torch.cuda.set_device(0)
+    sampler = ClockSampler()
+    sampler.start()
     peak, peak_source = peaks()
     config = dict(M2, num_hidden_layers=args.layers)
     largest = max(args.batch, 1 if args.skip_points else 64)
@@ -164,17 +166,8 @@ def main() -> int:
         return slots, first
 
     def device_step(slots, tokens_dev):
-        """One decode step whose tokens come from and go to the device."""
-        starts = [engine.cache.length(s) for s in slots]
-        ones = [1] * len(slots)
-        engine.cache.begin_step(slots, ones)
-        ctx = StepContext(engine.workspace, model.dtype, slots, starts, ones)
-        rows = torch.arange(len(slots), dtype=torch.int32, device="cuda")
-        logits = model.forward(ctx, engine.cache, tokens_dev, rows)
-        engine.cache.end_step(slots, ones)
-        out = torch.empty(len(slots), dtype=torch.int32, device="cuda")
-        ops.sample_rows(logits, None, None, out)
-        return out
+        """One decode step whose tokens come from and go to the device (the engine's recorded step)."""
+        return engine.pick_on_device(engine.step_on_device(slots, tokens_dev))
 
     def time_decode(slots, first, steps, warmup):
         tokens = first
@@ -196,8 +189,10 @@ def main() -> int:
         picked: list[int] = []
         for block in model.blocks:
             block.feed_forward.on_route = lambda ids: picked.append(int(torch.unique(ids).numel()))
-        probe = torch.randint(0, cfg.vocab_size, (len(slots),), dtype=torch.int32, device="cuda")
-        device_step(slots, probe)
+        probe = rng.integers(0, cfg.vocab_size, size=len(slots)).tolist()
+        recording, engine.record_steps = engine.record_steps, False        # the count needs a step run directly
+        engine.step(slots, [[t] for t in probe])
+        engine.record_steps = recording
         torch.cuda.synchronize()
         for block in model.blocks:
             block.feed_forward.on_route = None
@@ -210,13 +205,12 @@ def main() -> int:
         return weights + kv, picked
 
     result: dict = {}
-    sampler = ClockSampler()
 
     # ---- the headline: decode at --batch ------------------------------------------------------------------
     slots, first = fill(args.batch, real=True)
-    sampler.start()
+    timed_from = time.time()
     ms_step, launches, tokens = time_decode(slots, first, args.steps, args.warmup)
-    clocks = sampler.stop()
+    clocks = sampler.window(timed_from, time.time())
     value = args.batch * 1000.0 / ms_step
     step_bytes, picked = decode_bytes(slots)
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
@@ -289,6 +283,7 @@ def main() -> int:
         points[f"decode_b{args.batch}"] = round(value, 2)
         result["points"] = points
 
+    sampler.stop()
     print(json.dumps(result))
     return 0
 

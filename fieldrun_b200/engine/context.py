@@ -36,9 +36,26 @@ class Workspace:
         return sum(t.numel() * t.element_size() for t in self._store.values())
 
 
+def pack_tables(slots: Sequence[int], starts: Sequence[int], q_lens: Sequence[int]) -> np.ndarray:
+    """The step's tables as one int32 array: per token position, slot and sequence; per sequence slot, start
+    and number of new tokens; then the running sum of the new tokens."""
+    q = np.asarray(q_lens, dtype=np.int64)
+    cu = np.concatenate([[0], np.cumsum(q)])
+    seq_of_tok = np.repeat(np.arange(len(q)), q)
+    within = np.arange(int(q.sum())) - np.repeat(cu[:-1], q)
+    pos = np.repeat(np.asarray(starts, dtype=np.int64), q) + within
+    slot_of_tok = np.repeat(np.asarray(slots, dtype=np.int64), q)
+    return np.concatenate([pos, slot_of_tok, seq_of_tok, np.asarray(slots, dtype=np.int64),
+                           np.asarray(starts, dtype=np.int64), q, cu]).astype(np.int32)
+
+
 class StepContext:
     def __init__(self, workspace: Workspace, dtype: torch.dtype, slots: Sequence[int], starts: Sequence[int],
-                 q_lens: Sequence[int]):
+                 q_lens: Sequence[int], *, tables: torch.Tensor | None = None, max_kv_len: int | None = None):
+        """``tables`` (optional) is a device buffer that already holds, or will hold before the kernels run,
+        what :func:`pack_tables` makes for this step; it is used instead of a fresh transfer, so that a
+        recorded step can be run again with other positions and slots.  ``max_kv_len`` then bounds the
+        lengths the recorded step may be run with."""
         self.workspace = workspace
         self.device = workspace.device
         self.dtype = dtype
@@ -49,23 +66,17 @@ class StepContext:
         self.num_tokens = int(sum(self.seq_q_lens))
         self.max_q_len = max(self.seq_q_lens, default=0)
         self.max_kv_len = max((s + q for s, q in zip(self.seq_starts, self.seq_q_lens)), default=0)
+        if max_kv_len is not None:
+            self.max_kv_len = max(self.max_kv_len, int(max_kv_len))
         self.is_decode = self.max_q_len == 1 and self.num_tokens == self.num_seqs
-        q = np.asarray(self.seq_q_lens, dtype=np.int64)
-        self.cu_q_lens = np.concatenate([[0], np.cumsum(q)]).astype(np.int32)
-        seq_of_tok = np.repeat(np.arange(self.num_seqs, dtype=np.int32), q)
-        within = np.arange(self.num_tokens, dtype=np.int64) - np.repeat(self.cu_q_lens[:-1].astype(np.int64), q)
-        pos = np.repeat(np.asarray(self.seq_starts, dtype=np.int64), q) + within
-        slot_of_tok = np.repeat(np.asarray(self.seq_slots, dtype=np.int32), q)
-        self.host_tok_pos = pos.astype(np.int32)
-        self.host_tok_seq = seq_of_tok
-        # one transfer for all the tables
-        packed = np.concatenate([
-            self.host_tok_pos, slot_of_tok, seq_of_tok,
-            np.asarray(self.seq_slots, dtype=np.int32), np.asarray(self.seq_starts, dtype=np.int32),
-            np.asarray(self.seq_q_lens, dtype=np.int32), self.cu_q_lens,
-        ]).astype(np.int32)
-        dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
         t, b = self.num_tokens, self.num_seqs
+        if tables is None:
+            # one transfer for all the tables
+            dev = torch.from_numpy(pack_tables(self.seq_slots, self.seq_starts, self.seq_q_lens)).to(self.device)
+        else:
+            dev = tables
+            if dev.numel() != 3 * t + 4 * b + 1 or dev.dtype != torch.int32:
+                raise ValueError("the step's table buffer has the wrong size")
         self.tok_pos = dev[0:t]
         self.tok_slot = dev[t:2 * t]
         self.tok_seq = dev[2 * t:3 * t]

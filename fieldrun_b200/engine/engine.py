@@ -17,16 +17,59 @@ import torch
 
 from ..cache import SequenceCache
 from ..csrc import ops
-from .context import StepContext, Workspace
+from .context import StepContext, Workspace, pack_tables
 from .model import DecoderModel
+
+RECORD_KV_STEP = 1024          # a recorded step serves lengths up to the next multiple of this
+RECORDED_STEPS_KEPT = 6
 
 
 class StepError(ValueError):
     """A step was asked for that cannot be run (bad token id, unknown slot, wanted place out of range)."""
 
 
+class _RecordedStep:
+    """One decode step (one token for each of ``batch`` sequences) recorded as a CUDA graph.
+
+    Its inputs live in fixed device buffers: the tokens, and the step's tables (positions, slots).  Running
+    it again means copying new tokens and tables into those buffers and launching the graph; the page
+    tables are the cache's own device tensors, which the cache keeps up to date.  Launch overhead of the
+    step's many small kernels disappears, which is most of a small batch's step time."""
+
+    def __init__(self, engine: "Engine", batch: int, kv_cap: int):
+        self.batch, self.kv_cap = batch, kv_cap
+        count = 3 * batch + 4 * batch + 1
+        self.host = torch.empty(batch + count, dtype=torch.int32).pin_memory()
+        self.inputs = torch.zeros(batch + count, dtype=torch.int32, device=engine.device)
+        self.tokens = self.inputs[:batch]
+        self.tables = self.inputs[batch:]
+        self.rows = torch.arange(batch, dtype=torch.int32, device=engine.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels = 0                                   # kernels of this library inside the graph
+        self.logits: Optional[torch.Tensor] = None
+        # scratch of its own: the graph holds the addresses, so no other step may ever move these buffers
+        self.workspace = Workspace(engine.device)
+        self.ctx = StepContext(self.workspace, engine.model.dtype, [0] * batch, [0] * batch, [1] * batch,
+                               tables=self.tables, max_kv_len=kv_cap)
+        self.copied = torch.cuda.Event()
+
+    def load(self, tokens, slots: Sequence[int], starts: Sequence[int]) -> None:
+        """New inputs: ``tokens`` from the host (numpy) or already on the device (tensor)."""
+        self.copied.synchronize()                          # the last copy out of the pinned buffer is done
+        self.host[self.batch:] = torch.from_numpy(pack_tables(slots, starts, [1] * self.batch))
+        if isinstance(tokens, torch.Tensor):
+            self.tables.copy_(self.host[self.batch:], non_blocking=True)
+            if tokens.data_ptr() != self.tokens.data_ptr():
+                self.tokens.copy_(tokens)
+        else:
+            self.host[:self.batch] = torch.from_numpy(np.asarray(tokens).astype(np.int32))
+            self.inputs.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+
 class Engine:
-    def __init__(self, model: DecoderModel, *, max_tokens: int, num_slots: Optional[int] = None, device="cuda"):
+    def __init__(self, model: DecoderModel, *, max_tokens: int, num_slots: Optional[int] = None, device="cuda",
+                 record_steps: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("fieldrun_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.model = model
@@ -36,6 +79,9 @@ class Engine:
         self.workspace = Workspace(self.device)
         self.vocab_size = model.plan.vocab_size
         self.steps_run = 0
+        self.record_steps = record_steps and model.replayable
+        self._recorded: dict[tuple[int, int], _RecordedStep] = {}
+        self.steps_replayed = 0
 
     # -- sequences -------------------------------------------------------------------------------------
     def new_sequence(self) -> int:
@@ -94,6 +140,11 @@ class Engine:
                             f"{self.cache.max_tokens}")
 
         self.cache.begin_step(slots, q_lens)               # raises before anything is launched
+        if self.record_steps and max(q_lens) == 1 and rows == list(range(len(slots))):
+            logits = self._recorded_step(slots, flat, starts)
+            self.cache.end_step(slots, q_lens)
+            self.steps_run += 1
+            return logits
         ctx = StepContext(self.workspace, self.model.dtype, slots, starts, q_lens)
         tokens_dev = torch.from_numpy(flat.astype(np.int32)).to(self.device)
         rows_dev = torch.tensor(rows, dtype=torch.int32, device=self.device) if rows else None
@@ -101,6 +152,64 @@ class Engine:
         self.cache.end_step(slots, q_lens)
         self.steps_run += 1
         return logits
+
+    def step_on_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One more token for each sequence, the tokens being an int32 tensor on the device (the previous
+        step's picks, say): no token crosses to the host.  Returns the logits of every sequence."""
+        if tokens.dtype != torch.int32 or tokens.numel() != len(slots) or not tokens.is_cuda:
+            raise StepError("step_on_device takes one int32 token per sequence, on the device")
+        ones = [1] * len(slots)
+        starts = [self.cache.length(s) for s in slots]
+        if max(starts) + 1 > self.cache.max_tokens:
+            raise StepError(f"a sequence would pass position {self.cache.max_tokens}, where the position tables end")
+        self.cache.begin_step(slots, ones)
+        if self.record_steps:
+            logits = self._recorded_step(slots, tokens, starts, keep=False)
+        else:
+            ctx = StepContext(self.workspace, self.model.dtype, slots, starts, ones)
+            rows = torch.arange(len(slots), dtype=torch.int32, device=self.device)
+            logits = self.model.forward(ctx, self.cache, tokens.contiguous(), rows)
+        self.cache.end_step(slots, ones)
+        self.steps_run += 1
+        return logits
+
+    def pick_on_device(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The largest logit of every row, as an int32 tensor on the device."""
+        if out is None:
+            out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        ops.sample_rows(logits, None, None, out)
+        return out
+
+    def _recorded_step(self, slots: Sequence[int], tokens, starts: Sequence[int], keep: bool = True) -> torch.Tensor:
+        """A step of one token per sequence with the logits of every sequence wanted: recorded at its first
+        occurrence for this batch size and length range, replayed afterwards.  With ``keep`` the logits are
+        copied out of the recorded step's own buffer, which the next replay overwrites."""
+        batch = len(slots)
+        longest = max(starts) + 1
+        kv_cap = min((longest + RECORD_KV_STEP - 1) // RECORD_KV_STEP * RECORD_KV_STEP, self.cache.max_tokens)
+        key = (batch, kv_cap)
+        step = self._recorded.get(key)
+        if step is None:
+            if len(self._recorded) >= RECORDED_STEPS_KEPT:
+                self._recorded.pop(next(iter(self._recorded)))
+            step = self._recorded[key] = _RecordedStep(self, batch, kv_cap)
+        step.load(tokens, slots, starts)
+        if step.graph is None:
+            # run it directly this once (this also sizes every scratch buffer), then record it for the next times
+            logits = self.model.forward(step.ctx, self.cache, step.tokens, step.rows).clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches()
+            with torch.cuda.graph(graph):
+                step.logits = self.model.forward(step.ctx, self.cache, step.tokens, step.rows)
+            step.kernels = ops.launches() - before
+            ops.count_launches(-step.kernels)              # recorded, not run
+            step.graph = graph
+            return logits
+        step.graph.replay()
+        ops.count_launches(step.kernels)
+        self.steps_replayed += 1
+        return step.logits.clone() if keep else step.logits
 
     # -- picking tokens ------------------------------------------------------------------------------------
     def pick(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,

@@ -82,6 +82,11 @@ class DecoderModel:
             self.head.load(source)
         self.loaded = True
 
+    @property
+    def replayable(self) -> bool:
+        """Whether a step of this model can be recorded once and run again (see ``Part.replayable``)."""
+        return all(part.replayable for part in self.all_parts())
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
         for part in self.all_parts():

@@ -22,6 +22,8 @@ from .linear import linear
 
 
 class GQAAttention(Mixer):
+    replayable = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         a = spec.args

@@ -31,7 +31,14 @@ from ..weights.loader import TensorNeed, TensorSource
 
 
 class Part:
-    """Base of all parts: constants in, tensors by name, rows through."""
+    """Base of all parts: constants in, tensors by name, rows through.
+
+    ``replayable`` says that the part's ``forward`` reads the step's tables only on the device
+    (``ctx.tok_pos`` and the like, never the host lists) and makes every decision from shapes.  A step of
+    such parts can be recorded once as a CUDA graph and run again with other positions and slots.  A part
+    that leaves it False is always run directly."""
+
+    replayable: bool = False
 
     def __init__(self, spec: PartSpec, dtype: torch.dtype):
         self.spec = spec

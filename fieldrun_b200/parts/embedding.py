@@ -14,6 +14,8 @@ from .linear import linear
 
 
 class TokenEmbedding(Part):
+    replayable = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.vocab_size = int(spec.args["vocab_size"])
@@ -33,6 +35,8 @@ class TokenEmbedding(Part):
 
 
 class VocabHead(Part):
+    replayable = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.vocab_size = int(spec.args["vocab_size"])

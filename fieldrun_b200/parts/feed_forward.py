@@ -25,6 +25,7 @@ TILE_ROWS = 32        # rows of one expert that a block of the expert kernels ta
 
 class RoutedExperts(FeedForward):
     wants_float32_input = True          # the router reads the normed rows before they are rounded
+    replayable = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -148,6 +149,8 @@ class RoutedExperts(FeedForward):
 
 class DenseGatedUnit(FeedForward):
     """silu(x W_gate^T) * (x W_up^T), then W_down: one expert's formula for every row (src/minimax.rs:116-120)."""
+
+    replayable = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)

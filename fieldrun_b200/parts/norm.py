@@ -13,6 +13,8 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    replayable = True
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.width = int(spec.args["width"])
