@@ -48,7 +48,7 @@ FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype
 
 // ----------------------------------------------------------------------------- RMSNorm (+ residual add)
 
-#define NORM_BLOCK 256
+#define NORM_BLOCK 1024
 
 // One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]); if write_back the
 // sum is stored to x[src] (the residual stream).  out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and,

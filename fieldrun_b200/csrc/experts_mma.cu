@@ -27,25 +27,32 @@ __device__ __forceinline__ uint4 load_stream(const void* ptr) {
     return v;
 }
 
-#define EM_WARPS 4           // warps per block, 16 features each
+#define EM_GROUPS 4          // groups of 16 features per block; a block has EM_GROUPS * splits warps
 
 // grid (row tile, block of 64 features).  NB column blocks of 8 rows each: the tile has at most 8 NB rows.
+// The block's warps are (feature group, k split): with few tiles (a batch of one, or a dense layer as a
+// single "expert") the inner dimension is cut into blockDim / 128 parts, so that enough loads are in
+// flight; the parts are added in the order of k, by the warps of the first part, through shared memory.
 template <int NB, bool PAIRED, typename OutT>
-__global__ void __launch_bounds__(EM_WARPS * 32)
+__global__ void __launch_bounds__(512 / NB)
 expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, const int* __restrict__ x_rows,
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                       const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out, int F, int K) {
+                       const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out, int F, int K,
+                       int k_per_split) {
+    extern __shared__ float partial[];       // [splits - 1][EM_GROUPS][NACC][32]
+    constexpr int NACC = NB * 4 * (PAIRED ? 2 : 1);
     const int tile = blockIdx.x;
     if (tile >= num_tiles[0]) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int f0 = (blockIdx.y * EM_WARPS + warp) * 16;
-    if (f0 >= F) return;
+    const int group = warp & (EM_GROUPS - 1), split = warp / EM_GROUPS, splits = blockDim.x / (32 * EM_GROUPS);
+    const int f0 = (blockIdx.y * EM_GROUPS + group) * 16;
+    const bool active = f0 < F;
     const int e = tile_expert[tile];
     const int row0 = tile_row0[tile];
     const int rows = min(NB * 8, offsets[e + 1] - row0);
     const int blocks = (rows + 7) >> 3;
     const size_t f_total = PAIRED ? (size_t)2 * F : (size_t)F;
-    const bf16* wg0 = W + ((size_t)e * f_total + f0 + g) * K + 8 * t;      // feature f0 + g
+    const bf16* wg0 = W + ((size_t)e * f_total + (active ? f0 : 0) + g) * K + 8 * t;      // feature f0 + g
     const bf16* wg1 = wg0 + (size_t)8 * K;                                 // feature f0 + g + 8
     const bf16* wu0 = wg0 + (size_t)F * K;                                 // the up rows of the same features
     const bf16* wu1 = wg1 + (size_t)F * K;
@@ -63,12 +70,14 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
         for (int i = 0; i < 4; ++i) { acc_g[j][i] = 0.f; if (PAIRED) acc_u[j][i] = 0.f; }
 
     constexpr int UNROLL = NB == 1 ? 4 : 2;
+    const int k_begin = split * k_per_split;
+    const int k_end = active ? min(K, k_begin + k_per_split) : k_begin;
 #pragma unroll 1
-    for (int k0 = 0; k0 < K; k0 += 32 * UNROLL) {
+    for (int k0 = k_begin; k0 < k_end; k0 += 32 * UNROLL) {
         uint4 a_g0[UNROLL], a_g1[UNROLL], a_u0[PAIRED ? UNROLL : 1], a_u1[PAIRED ? UNROLL : 1];
 #pragma unroll
         for (int s = 0; s < UNROLL; ++s) {
-            if (k0 + 32 * s < K) {
+            if (k0 + 32 * s < k_end) {
                 a_g0[s] = load_stream(wg0 + k0 + 32 * s);
                 a_g1[s] = load_stream(wg1 + k0 + 32 * s);
                 if (PAIRED) { a_u0[s] = load_stream(wu0 + k0 + 32 * s); a_u1[s] = load_stream(wu1 + k0 + 32 * s); }
@@ -76,7 +85,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
         }
 #pragma unroll
         for (int s = 0; s < UNROLL; ++s) {
-            if (k0 + 32 * s < K) {
+            if (k0 + 32 * s < k_end) {
 #pragma unroll
                 for (int j = 0; j < NB; ++j) {
                     if (j < blocks) {
@@ -92,6 +101,31 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
             }
         }
     }
+    if (splits > 1) {
+        if (split > 0) {
+            float* mine = partial + ((size_t)(split - 1) * EM_GROUPS + group) * NACC * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    mine[(j * 4 + i) * 32] = acc_g[j][i];
+                    if (PAIRED) mine[(NB * 4 + j * 4 + i) * 32] = acc_u[j][i];
+                }
+        }
+        __syncthreads();
+        if (split > 0) return;
+        for (int s = 1; s < splits; ++s) {
+            const float* theirs = partial + ((size_t)(s - 1) * EM_GROUPS + group) * NACC * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc_g[j][i] += theirs[(j * 4 + i) * 32];
+                    if (PAIRED) acc_u[j][i] += theirs[(NB * 4 + j * 4 + i) * 32];
+                }
+        }
+    }
+    if (!active) return;
     // accumulator (i): feature f0 + g + 8 (i >> 1), row 8 j + 2 t + (i & 1)
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
@@ -109,22 +143,29 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
 
 // W bf16 [E][(paired ? 2 : 1) F][K]; X bf16 rows of K; tiles of at most tile_rows (8, 16 or 32) rows.
 // paired: out bf16 [N, F] = silu(x W1^T) * (x W3^T); else out float32 [N, F] = x W^T.
+// splits: parts the inner size is cut into within a block (1 when there are many tiles).
 FRB_API int frb_expert_gemm_mma(const void* W, const void* X, const int* x_rows, const int* tile_expert, const int* tile_row0,
                                 const int* num_tiles, const int* offsets, int max_tiles, int tile_rows, void* out, int F, int K,
-                                int paired, cudaStream_t stream) {
+                                int paired, int splits, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     FRB_CHECK_ARG(K % 32 == 0 && K > 0, "expert stream: inner size %d is not a multiple of 32", K);
     FRB_CHECK_ARG(F % 16 == 0 && F > 0, "expert stream: %d features are not a multiple of 16", F);
     FRB_CHECK_ARG(tile_rows == 8 || tile_rows == 16 || tile_rows == 32, "expert stream: tiles of %d rows", tile_rows);
-    dim3 grid(max_tiles, (F + 16 * EM_WARPS - 1) / (16 * EM_WARPS));
+    const int nb = tile_rows / 8;
+    FRB_CHECK_ARG(splits >= 1 && splits * nb <= 4, "expert stream: %d splits of the inner size with tiles of %d rows", splits,
+                  tile_rows);
+    const int k_per_split = ((K + splits - 1) / splits + 127) / 128 * 128;
+    dim3 grid(max_tiles, (F + 16 * EM_GROUPS - 1) / (16 * EM_GROUPS));
     FRB_CHECK_ARG(grid.y <= 65535, "expert stream: %d features exceed the grid", F);
+    const int threads = 32 * EM_GROUPS * splits;
+    const size_t smem = (size_t)(splits - 1) * EM_GROUPS * nb * 4 * (paired ? 2 : 1) * 32 * sizeof(float);
 #define LAUNCH(NB)                                                                                                        \
     if (paired)                                                                                                           \
-        expert_gemm_mma_kernel<NB, true, bf16><<<grid, EM_WARPS * 32, 0, stream>>>(                                       \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K);        \
+        expert_gemm_mma_kernel<NB, true, bf16><<<grid, threads, smem, stream>>>(                                          \
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split); \
     else                                                                                                                  \
-        expert_gemm_mma_kernel<NB, false, float><<<grid, EM_WARPS * 32, 0, stream>>>(                                     \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K)
+        expert_gemm_mma_kernel<NB, false, float><<<grid, threads, smem, stream>>>(                                        \
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split)
     if (tile_rows == 8) { LAUNCH(1); } else if (tile_rows == 16) { LAUNCH(2); } else { LAUNCH(4); }
 #undef LAUNCH
     FRB_RETURN_LAUNCH("expert_gemm_mma");

@@ -33,7 +33,8 @@ _SIGNATURES = {
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifii",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
-    "frb_expert_gemm_mma": "pppppppiipiii",
+    "frb_expert_gemm_mma": "pppppppiipiiii",
+    "frb_route_plan_small": "ppiiiifipppppppp",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -278,11 +279,33 @@ def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 
 def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
                     tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
-                    tile_rows: int, out: torch.Tensor, *, paired: bool) -> None:
-    """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows)."""
+                    tile_rows: int, out: torch.Tensor, *, paired: bool, splits: int = 1) -> None:
+    """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows; ``splits`` parts of
+    the inner size per block, splits * tile_rows <= 32)."""
     _want(w, torch.bfloat16, "streamed expert weights")
     _want(x, torch.bfloat16, "streamed expert inputs")
     _want(out, torch.bfloat16 if paired else torch.float32, "streamed expert outputs")
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_mma", _ptr(w), _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
-          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired))
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits))
+
+
+SMALL_ROUTE_ASSIGNMENTS = 1024
+
+
+def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,
+                     tile_rows: int, ids: torch.Tensor, weights: torch.Tensor, offsets: torch.Tensor,
+                     sorted_token: torch.Tensor, row_of_assign: torch.Tensor, tile_expert: torch.Tensor,
+                     tile_row0: torch.Tensor, num_tiles: torch.Tensor) -> None:
+    """Expert choice and expert-sorted lists in one launch, for steps of at most 1024 (token, expert) pairs."""
+    _want(logits, torch.float32, "router logits")
+    tokens, experts = logits.shape
+    _call("frb_route_plan_small", _ptr(logits), _ptr(bias), tokens, experts, top_k, int(renormalize), float(routed_scale),
+          tile_rows, _ptr(ids), _ptr(weights), _ptr(offsets), _ptr(sorted_token), _ptr(row_of_assign), _ptr(tile_expert),
+          _ptr(tile_row0), _ptr(num_tiles))
+
+
+def stream_splits(tiles: int, features: int, tile_rows: int) -> int:
+    """Parts to cut the inner size into so that about 2048 warps stream weights (see the kernel's note)."""
+    groups = max(1, tiles * ((features + 15) // 16))
+    return max(1, min(4 // (tile_rows // 8), -(-2048 // groups)))

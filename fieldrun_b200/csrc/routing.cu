@@ -9,15 +9,10 @@
 
 // ----------------------------------------------------------------------------- top-k choice
 
-// One warp per token.  logits [T, E] float32 -> ids [T, k] (rank order), weights [T, k].
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_experts,
-                                   int top_k, int renormalize, float routed_scale, int* __restrict__ ids,
-                                   float* __restrict__ weights) {
-    extern __shared__ float sm[];
-    float* score = sm;                    // [E]
-    float* choice = sm + num_experts;     // [E]
-    const int t = blockIdx.x, lane = threadIdx.x;
-    const float* z = logits + (size_t)t * num_experts;
+// One warp picks one token's experts.  z: the token's E logits; score/choice: E floats of scratch each.
+__device__ __forceinline__ void pick_experts(const float* __restrict__ z, const float* __restrict__ bias, int num_experts,
+                                             int top_k, int renormalize, float routed_scale, float* score, float* choice,
+                                             int* __restrict__ ids, float* __restrict__ weights, int lane) {
     for (int e = lane; e < num_experts; e += 32) {
         const float s = 1.0f / (1.0f + expf(-z[e]));
         score[e] = s;
@@ -44,8 +39,8 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
         }
         __syncwarp();
         if (lane == 0) {
-            ids[(size_t)t * top_k + r] = best_e;
-            weights[(size_t)t * top_k + r] = score[best_e];
+            ids[r] = best_e;
+            weights[r] = score[best_e];
             choice[best_e] = -INFINITY;
         }
         denom += score[best_e];
@@ -53,11 +48,22 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
     }
     if (lane == 0) {
         for (int r = 0; r < top_k; ++r) {
-            float w = weights[(size_t)t * top_k + r];
+            float w = weights[r];
             if (renormalize) w = w / denom;               // s_e / sum of picked s (src/minimax.rs:100-103)
-            weights[(size_t)t * top_k + r] = w * routed_scale;
+            weights[r] = w * routed_scale;
         }
     }
+    __syncwarp();
+}
+
+// One warp per token.  logits [T, E] float32 -> ids [T, k] (rank order), weights [T, k].
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_experts,
+                                   int top_k, int renormalize, float routed_scale, int* __restrict__ ids,
+                                   float* __restrict__ weights) {
+    extern __shared__ float sm[];
+    const int t = blockIdx.x;
+    pick_experts(logits + (size_t)t * num_experts, bias, num_experts, top_k, renormalize, routed_scale, sm, sm + num_experts,
+                 ids + (size_t)t * top_k, weights + (size_t)t * top_k, threadIdx.x);
 }
 
 FRB_API int frb_router_topk(const float* logits, const float* bias, int num_tokens, int num_experts, int top_k,
@@ -167,25 +173,122 @@ FRB_API int frb_expert_plan(const int* ids, int num_tokens, int top_k, int num_e
     FRB_RETURN_LAUNCH("expert_plan");
 }
 
+// ----------------------------------------------------------------------------- choice and work lists in one block
+
+#define SMALL_WARPS 16
+#define SMALL_MAX_ASSIGN 1024
+
+// For steps of few tokens (T * k <= 1024): one block picks every token's experts (a warp per token, in
+// turn), then sorts the assignments by expert and writes the same lists as the three kernels above.
+__global__ void __launch_bounds__(SMALL_WARPS * 32)
+route_plan_small_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_tokens, int num_experts,
+                        int top_k, int renormalize, float routed_scale, int tile_rows, int* __restrict__ ids,
+                        float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ sorted_token,
+                        int* __restrict__ row_of_assign, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                        int* __restrict__ num_tiles) {
+    extern __shared__ float sm[];
+    __shared__ int s_ids[SMALL_MAX_ASSIGN];
+    float* scratch = sm;                                                 // [SMALL_WARPS][2][E]
+    int* count = reinterpret_cast<int*>(sm + (size_t)SMALL_WARPS * 2 * num_experts);   // [E]
+    int* first = count + num_experts;                                    // [E + 1]
+    int* first_tile = first + num_experts + 1;                           // [E + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int num_assign = num_tokens * top_k;
+    for (int t = warp; t < num_tokens; t += SMALL_WARPS)
+        pick_experts(logits + (size_t)t * num_experts, bias, num_experts, top_k, renormalize, routed_scale,
+                     scratch + (size_t)warp * 2 * num_experts, scratch + (size_t)warp * 2 * num_experts + num_experts,
+                     ids + (size_t)t * top_k, weights + (size_t)t * top_k, lane);
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int a = threadIdx.x; a < num_assign; a += blockDim.x) {
+        const int e = ids[a];                                            // written by this block, above
+        s_ids[a] = e;
+        atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {                                                     // exclusive sums over the experts
+        const int per_lane = (num_experts + 31) / 32;
+        const int begin = lane * per_lane, end = min(num_experts, begin + per_lane);
+        int rows = 0, tiles = 0;
+        for (int e = begin; e < end; ++e) { rows += count[e]; tiles += (count[e] + tile_rows - 1) / tile_rows; }
+        int rows_before = rows, tiles_before = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, rows_before, o), c = __shfl_up_sync(0xffffffffu, tiles_before, o);
+            if (lane >= o) { rows_before += r; tiles_before += c; }
+        }
+        const int total_rows = __shfl_sync(0xffffffffu, rows_before, 31), total_tiles = __shfl_sync(0xffffffffu, tiles_before, 31);
+        rows_before -= rows;
+        tiles_before -= tiles;
+        for (int e = begin; e < end; ++e) {
+            first[e] = rows_before;
+            first_tile[e] = tiles_before;
+            rows_before += count[e];
+            tiles_before += (count[e] + tile_rows - 1) / tile_rows;
+        }
+        if (lane == 0) { first[num_experts] = total_rows; num_tiles[0] = total_tiles; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) offsets[e] = first[e];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int tile = first_tile[e];
+        for (int r = 0; r < count[e]; r += tile_rows, ++tile) {
+            tile_expert[tile] = e;
+            tile_row0[tile] = first[e] + r;
+        }
+        int at = first[e];
+        if (count[e] > 0) {
+            for (int a = 0; a < num_assign; ++a) {
+                if (s_ids[a] == e) {
+                    sorted_token[at] = a / top_k;
+                    row_of_assign[a] = at;
+                    ++at;
+                }
+            }
+        }
+    }
+}
+
+// logits [T, E] -> ids, weights and the expert-sorted lists, for T * k <= 1024, in one launch.
+FRB_API int frb_route_plan_small(const float* logits, const float* bias, int num_tokens, int num_experts, int top_k,
+                                 int renormalize, float routed_scale, int tile_rows, int* ids, float* weights, int* offsets,
+                                 int* sorted_token, int* row_of_assign, int* tile_expert, int* tile_row0, int* num_tiles,
+                                 cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "router: top_k %d is outside 1..%d experts", top_k, num_experts);
+    FRB_CHECK_ARG(num_tokens * top_k <= SMALL_MAX_ASSIGN, "small router: %d assignments exceed %d", num_tokens * top_k,
+                  SMALL_MAX_ASSIGN);
+    const size_t smem = (size_t)SMALL_WARPS * 2 * num_experts * sizeof(float) + (size_t)(3 * num_experts + 2) * sizeof(int);
+    FRB_CHECK_ARG(smem <= 160 * 1024, "small router: %d experts need %zu bytes of shared memory", num_experts, smem);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(route_plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    route_plan_small_kernel<<<1, SMALL_WARPS * 32, smem, stream>>>(logits, bias, num_tokens, num_experts, top_k, renormalize,
+                                                                   routed_scale, tile_rows, ids, weights, offsets, sorted_token,
+                                                                   row_of_assign, tile_expert, tile_row0, num_tiles);
+    FRB_RETURN_LAUNCH("route_plan_small");
+}
+
 // ----------------------------------------------------------------------------- weighted sum of expert outputs
 
 // out[t, :] = sum_{r < k} w[t, r] * y[row_of_assign[t*k + r], :], added in rank order.
 __global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
                                const int* __restrict__ row_of_assign, int top_k, int width, float* __restrict__ out) {
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float acc = 0.f;
-        for (int r = 0; r < top_k; ++r) {
-            const int row = row_of_assign[(size_t)t * top_k + r];
-            acc += weights[(size_t)t * top_k + r] * y[(size_t)row * width + c];
-        }
-        out[(size_t)t * width + c] = acc;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    float acc = 0.f;
+    for (int r = 0; r < top_k; ++r) {
+        const int row = row_of_assign[(size_t)t * top_k + r];
+        acc += weights[(size_t)t * top_k + r] * y[(size_t)row * width + c];
     }
+    out[(size_t)t * width + c] = acc;
 }
 
 FRB_API int frb_expert_combine(const float* y, const float* weights, const int* row_of_assign, int num_tokens, int top_k,
                                int width, float* out, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
-    combine_kernel<<<num_tokens, 256, 0, stream>>>(y, weights, row_of_assign, top_k, width, out);
+    dim3 grid(num_tokens, (width + 255) / 256);
+    FRB_CHECK_ARG(grid.y <= 65535, "combine: a width of %d exceeds the grid", width);
+    combine_kernel<<<grid, 256, 0, stream>>>(y, weights, row_of_assign, top_k, width, out);
     FRB_RETURN_LAUNCH("expert_combine");
 }

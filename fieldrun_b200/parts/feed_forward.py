@@ -123,10 +123,13 @@ class RoutedExperts(FeedForward):
         hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
         y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
         if self.streams():
+            tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
             ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
-                                p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True)
+                                p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True,
+                                splits=ops.stream_splits(tiles, self.expert_width, p["tile_rows"]))
             ops.expert_gemm_mma(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
-                                p["max_tiles"], p["tile_rows"], y, paired=False)
+                                p["max_tiles"], p["tile_rows"], y, paired=False,
+                                splits=ops.stream_splits(tiles, self.hidden_size, p["tile_rows"]))
             return y
         ops.expert_gemm_generic(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
                                 p["offsets"], p["max_tiles"], hidden, paired=True)
@@ -134,13 +137,41 @@ class RoutedExperts(FeedForward):
                                 p["max_tiles"], y, paired=False)
         return y
 
+    def route_and_plan(self, ctx, act32: torch.Tensor):
+        """For steps of few tokens: choice and lists in one launch."""
+        tokens = act32.shape[0]
+        n = tokens * self.top_k
+        logits = linear(act32, self.router)
+        tile_rows = self.tile_rows(n)
+        max_tiles = (n + tile_rows - 1) // tile_rows + min(self.num_experts, n)
+        ids = ctx.buffer("experts.ids", (tokens, self.top_k), torch.int32)
+        weights = ctx.buffer("experts.weights", (tokens, self.top_k), torch.float32)
+        p = {
+            "offsets": ctx.buffer("experts.offsets", (self.num_experts + 1,), torch.int32),
+            "sorted_token": ctx.buffer("experts.sorted_token", (n,), torch.int32),
+            "row_of_assign": ctx.buffer("experts.row_of_assign", (n,), torch.int32),
+            "tile_expert": ctx.buffer("experts.tile_expert", (max_tiles,), torch.int32),
+            "tile_row0": ctx.buffer("experts.tile_row0", (max_tiles,), torch.int32),
+            "num_tiles": ctx.buffer("experts.num_tiles", (1,), torch.int32),
+            "max_tiles": max_tiles, "rows": n, "tile_rows": tile_rows,
+        }
+        ops.route_plan_small(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, tile_rows, ids, weights,
+                             p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"], p["tile_row0"],
+                             p["num_tiles"])
+        return ids, weights, p
+
     def forward(self, ctx, act, act32):
         if act32 is None:
             raise ValueError("routed experts need the normed rows in float32 for the router")
-        ids, weights = self.route(ctx, act32)
-        if self.on_route is not None:
-            self.on_route(ids)
-        p = self.plan(ctx, ids)
+        if act.shape[0] * self.top_k <= ops.SMALL_ROUTE_ASSIGNMENTS and self.num_experts <= 1024:
+            ids, weights, p = self.route_and_plan(ctx, act32)
+            if self.on_route is not None:
+                self.on_route(ids)
+        else:
+            ids, weights = self.route(ctx, act32)
+            if self.on_route is not None:
+                self.on_route(ids)
+            p = self.plan(ctx, ids)
         y = self.experts(ctx, act, p)
         out = ctx.buffer("experts.out", (act.shape[0], self.hidden_size), torch.float32)
         ops.expert_combine(y, weights, p["row_of_assign"], out)

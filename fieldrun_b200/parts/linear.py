@@ -13,6 +13,21 @@ from typing import Optional
 
 import torch
 
+from ..csrc import ops
+
+_ONE_TILE: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+STREAM_ROWS = 32          # up to this many rows a dense product is a stream over the weight (see experts_mma.cu)
+STREAM_FEATURES = 65536   # beyond this many output features the library product is at the memory roofline anyway
+
+
+def _one_tile(device: torch.device, rows: int):
+    key = (str(device), rows)
+    if key not in _ONE_TILE:
+        zero = torch.zeros(1, dtype=torch.int32, device=device)
+        _ONE_TILE[key] = (zero, zero.clone(), torch.ones(1, dtype=torch.int32, device=device),
+                          torch.tensor([0, rows], dtype=torch.int32, device=device))
+    return _ONE_TILE[key]
+
 
 def require_true_float32() -> None:
     """Switch off every reduced-precision mode of float32 matrix products."""
@@ -37,6 +52,18 @@ def linear(rows: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]
         if out is None:
             return torch.mm(rows, weight.t())
         return torch.mm(rows, weight.t(), out=out)
+    count, inner = rows.shape
+    features = weight.shape[0]
+    if count <= STREAM_ROWS and inner % 32 == 0 and features % 16 == 0 and features <= STREAM_FEATURES \
+            and rows.is_contiguous() and weight.is_contiguous():
+        # few rows: the weight is the traffic; stream it once through the kernel that streams expert weights,
+        # the dense layer being a single expert whose rows are all the rows
+        tile_rows = 8 if count <= 8 else 16 if count <= 16 else 32
+        tile_expert, tile_row0, num_tiles, offsets = _one_tile(rows.device, count)
+        result = out if out is not None else torch.empty((count, features), dtype=torch.float32, device=rows.device)
+        ops.expert_gemm_mma(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
+                            tile_rows, result, paired=False, splits=ops.stream_splits(1, features, tile_rows))
+        return result
     result = torch.mm(rows, weight.t(), out_dtype=torch.float32)
     if out is None:
         return result

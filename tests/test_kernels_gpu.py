@@ -490,3 +490,64 @@ def test_kernels_refuse_sizes_they_do_not_take():
                                    torch.zeros_like(q), num_heads=2, num_kv_heads=1, head_dim=48, scale=1.0, window=None, max_chunks=1)
     with pytest.raises(KernelError, match="no CPU path"):
         ops().embed_rows(torch.zeros(1, dtype=torch.int32), torch.zeros(2, 2), torch.zeros(1, 2))
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,tile_rows", [(1, 8, 256, 8), (64, 8, 256, 8), (128, 8, 256, 16), (7, 3, 11, 32),
+                                                            (300, 2, 5, 32), (5, 1, 1, 8)])
+def test_choice_and_lists_in_one_launch_equal_the_separate_kernels(tokens, top_k, experts, tile_rows):
+    rng = np.random.default_rng(15)
+    logits = dev(rng.normal(size=(tokens, experts)).astype(np.float32))
+    bias = dev((0.2 * rng.normal(size=experts)).astype(np.float32))
+    n = tokens * top_k
+    max_tiles = (n + tile_rows - 1) // tile_rows + min(experts, n)
+    i32 = lambda k: torch.full((k,), -7, dtype=torch.int32, device=DEV)
+
+    def buffers():
+        return dict(ids=torch.empty(tokens, top_k, dtype=torch.int32, device=DEV),
+                    weights=torch.empty(tokens, top_k, dtype=torch.float32, device=DEV), offsets=i32(experts + 1),
+                    sorted_token=i32(n), row_of_assign=i32(n), tile_expert=i32(max_tiles), tile_row0=i32(max_tiles),
+                    num_tiles=i32(1))
+
+    a, b = buffers(), buffers()
+    ops().router_topk(logits, bias, top_k, True, 1.0, a["ids"], a["weights"])
+    ops().expert_plan(a["ids"], experts, tile_rows, i32(((n + 1023) // 1024) * experts), a["offsets"], a["sorted_token"],
+                      a["row_of_assign"], a["tile_expert"], a["tile_row0"], a["num_tiles"])
+    ops().route_plan_small(logits, bias, top_k, True, 1.0, tile_rows, b["ids"], b["weights"], b["offsets"], b["sorted_token"],
+                           b["row_of_assign"], b["tile_expert"], b["tile_row0"], b["num_tiles"])
+    nt = int(a["num_tiles"].item())
+    assert nt == int(b["num_tiles"].item())
+    for name in ("ids", "weights", "offsets", "sorted_token", "row_of_assign"):
+        assert torch.equal(a[name], b[name]), name
+    for name in ("tile_expert", "tile_row0"):
+        assert torch.equal(a[name][:nt], b[name][:nt]), name
+
+
+@pytest.mark.parametrize("tile_rows,splits", [(8, 2), (8, 4), (16, 2)])
+def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits):
+    rng = np.random.default_rng(16)
+    experts, width, hidden, rows_per = 3, 96, 3072, [1, 0, tile_rows]
+    w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.05, torch.bfloat16)
+    x = dev(rng.normal(size=(9, hidden)), torch.bfloat16)
+    n = sum(rows_per)
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    sorted_token = rng.integers(0, 9, size=n).astype(np.int32)
+    tile_expert, tile_row0, num_tiles = np.array([0, 2], dtype=np.int32), np.array([0, 1], dtype=np.int32), np.array([2], dtype=np.int32)
+    outs = []
+    for s in (1, splits):
+        out = torch.full((n, width), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops().expert_gemm_mma(w13, x, dev(sorted_token), dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets), 2,
+                              tile_rows, out, paired=True, splits=s)
+        outs.append(f64(out))
+    xs, wf = f64(x), f64(w13)
+    expert_of = np.repeat(np.arange(experts), rows_per)
+    ref = np.stack([pm.silu(xs[sorted_token[r]] @ wf[expert_of[r], :width].T) * (xs[sorted_token[r]] @ wf[expert_of[r], width:].T)
+                    for r in range(n)])
+    close(outs[0], ref, 1e-2, "one part")
+    close(outs[1], ref, 1e-2, f"{splits} parts")
+    y = torch.empty(n, 80, dtype=torch.float32, device=DEV)
+    w = dev(rng.normal(size=(1, 80, hidden)) * 0.05, torch.bfloat16)
+    one = dev(np.array([0], dtype=np.int32))
+    x2 = dev(rng.normal(size=(n, hidden)), torch.bfloat16)
+    ops().expert_gemm_mma(w, x2, None, one, one, dev(np.array([1], dtype=np.int32)), dev(np.array([0, n], dtype=np.int32)),
+                          1, 32 if n > 16 else 16 if n > 8 else 8, y, paired=False, splits=1 if n > 16 else 2)
+    close(f64(y), f64(x2) @ f64(w)[0].T, 1e-5, "a dense layer as one expert")
