@@ -35,6 +35,8 @@ _SIGNATURES = {
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
     "frb_expert_gemm_mma": "pppppppiipiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
+    "frb_expert_gemm_tc": "pipippppiipiiip",
+    "frb_gather_rows_bf16": "pppii",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -309,3 +311,47 @@ def stream_splits(tiles: int, features: int, tile_rows: int) -> int:
     """Parts to cut the inner size into so that about 2048 warps stream weights (see the kernel's note)."""
     groups = max(1, tiles * ((features + 15) // 16))
     return max(1, min(4 // (tile_rows // 8), -(-2048 // groups)))
+
+
+_TC_STATUS: dict[str, torch.Tensor] = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """One int on the device that the tensor-core expert kernel sets when one of its waits gives up."""
+    key = str(device)
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def tc_status_check(device) -> None:
+    """Raise if a tensor-core expert kernel reported a wait that gave up since the last check (this reads
+    one int from the device, so it waits for the work before it)."""
+    key = str(device)
+    if key in _TC_STATUS:
+        code = int(_TC_STATUS[key].item())
+        if code != 0:
+            _TC_STATUS[key].zero_()
+            where = {1: "the producer waiting for a free stage", 2: "the MMA thread waiting for a loaded stage",
+                     3: "the epilogue waiting for the accumulators"}.get(code, f"code {code}")
+            raise KernelError(f"expert_gemm_tc: a wait gave up ({where}); the step's results are not valid")
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = x[rows[i]] for bfloat16 rows."""
+    _want(x, torch.bfloat16, "gathered rows")
+    _want(rows, torch.int32, "row indices")
+    _call("frb_gather_rows_bf16", _ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[-1])
+
+
+def expert_gemm_tc(w: torch.Tensor, x: torch.Tensor, tile_expert: torch.Tensor, tile_row0: torch.Tensor,
+                   num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int, tile_rows: int, out: torch.Tensor, *,
+                   paired: bool) -> None:
+    """The expert products on tcgen05 tensor cores; x holds the rows in expert-sorted order (tiles of 32, 64,
+    128 or 256 rows; features in steps of 128, inner size in steps of 64)."""
+    _want(w, torch.bfloat16, "expert weights")
+    _want(x, torch.bfloat16, "expert inputs")
+    _want(out, torch.bfloat16 if paired else torch.float32, "expert outputs")
+    feats = w.shape[1] // 2 if paired else w.shape[1]
+    _call("frb_expert_gemm_tc", _ptr(w), w.shape[0], _ptr(x), x.shape[0], _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), _ptr(tc_status(w.device)))

@@ -151,6 +151,8 @@ class Engine:
         logits = self.model.forward(ctx, self.cache, tokens_dev, rows_dev)
         self.cache.end_step(slots, q_lens)
         self.steps_run += 1
+        if ctx.num_tokens > len(slots):
+            ops.tc_status_check(self.device)          # a kernel that gave up on a wait must not pass for a result
         return logits
 
     def step_on_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:

@@ -21,6 +21,7 @@ from .base import FeedForward, register_part
 from .linear import linear
 
 TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
+TENSOR_CORE_ROWS_PER_EXPERT = 12     # above this many rows per expert (on average) a step runs on tcgen05
 
 
 class RoutedExperts(FeedForward):
@@ -88,12 +89,20 @@ class RoutedExperts(FeedForward):
         """Whether the tensor-core streaming kernel takes this part's sizes (bfloat16, sizes in steps of 32)."""
         return (self.dtype == torch.bfloat16 and self.hidden_size % 32 == 0 and self.expert_width % 32 == 0)
 
+    def on_tensor_cores(self, assignments: int) -> bool:
+        """Whether the tcgen05 kernel runs the step: bfloat16, sizes in steps of 128, and enough rows per
+        expert that the products, not the weights alone, are the work."""
+        return (self.dtype == torch.bfloat16 and self.hidden_size % 128 == 0 and self.expert_width % 128 == 0
+                and assignments > TENSOR_CORE_ROWS_PER_EXPERT * self.num_experts)
+
     def tile_rows(self, assignments: int) -> int:
         """Rows of one expert that one block takes: few when experts get few rows each, so that no block
-        carries accumulators it does not need."""
+        carries accumulators it does not need; enough that most experts fit one tile when they get many."""
+        per_expert = assignments / self.num_experts
+        if self.on_tensor_cores(assignments):
+            return next((t for t in (32, 64, 128, 256) if t >= 1.3 * per_expert), 256)
         if not self.streams():
             return TILE_ROWS
-        per_expert = assignments / self.num_experts
         return 8 if per_expert <= 4 else 16 if per_expert <= 12 else 32
 
     def plan(self, ctx, ids: torch.Tensor):
@@ -122,6 +131,14 @@ class RoutedExperts(FeedForward):
         """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order."""
         hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
         y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
+        if self.on_tensor_cores(p["rows"]):
+            gathered = ctx.buffer("experts.gathered", (p["rows"], self.hidden_size), self.dtype)
+            ops.gather_rows(act, p["sorted_token"], gathered)
+            ops.expert_gemm_tc(self.w13, gathered, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                               p["max_tiles"], p["tile_rows"], hidden, paired=True)
+            ops.expert_gemm_tc(self.w2, hidden, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                               p["max_tiles"], p["tile_rows"], y, paired=False)
+            return y
         if self.streams():
             tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
             ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],

@@ -551,3 +551,42 @@ def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits):
     ops().expert_gemm_mma(w, x2, None, one, one, dev(np.array([1], dtype=np.int32)), dev(np.array([0, n], dtype=np.int32)),
                           1, 32 if n > 16 else 16 if n > 8 else 8, y, paired=False, splits=1 if n > 16 else 2)
     close(f64(y), f64(x2) @ f64(w)[0].T, 1e-5, "a dense layer as one expert")
+
+
+@pytest.mark.parametrize("tile_rows", [32, 64, 128, 256])
+@pytest.mark.parametrize("experts,width,hidden,rows_per", [(3, 128, 256, [70, 0, 300]), (2, 256, 128, [1, 33]),
+                                                           (4, 1536, 3072, [64, 5, 0, 130])])
+def test_expert_products_on_tcgen05(tile_rows, experts, width, hidden, rows_per):
+    rng = np.random.default_rng(17)
+    w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.05, torch.bfloat16)
+    w2 = dev(rng.normal(size=(experts, hidden, width)) * 0.05, torch.bfloat16)
+    n = sum(rows_per)
+    x = dev(rng.normal(size=(n, hidden)), torch.bfloat16)                  # already in expert-sorted order
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    tiles = [(e, offsets[e] + r) for e in range(experts) for r in range(0, rows_per[e], tile_rows)]
+    tile_expert = np.array([t[0] for t in tiles] + [0, 0], dtype=np.int32)
+    tile_row0 = np.array([t[1] for t in tiles] + [0, 0], dtype=np.int32)
+    num_tiles = np.array([len(tiles)], dtype=np.int32)
+    hidden_out = torch.full((n, width), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops().expert_gemm_tc(w13, x, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets), len(tiles) + 2, tile_rows,
+                         hidden_out, paired=True)
+    ops().tc_status_check(DEV)
+    xs, w13f, w2f = f64(x), f64(w13), f64(w2)
+    expert_of = np.repeat(np.arange(experts), rows_per)
+    ref_h = np.stack([pm.silu(xs[r] @ w13f[expert_of[r], :width].T) * (xs[r] @ w13f[expert_of[r], width:].T) for r in range(n)])
+    close(f64(hidden_out), ref_h, 1e-2, "tcgen05 gate/up product")
+    y = torch.full((n, hidden), 9.0, dtype=torch.float32, device=DEV)
+    ops().expert_gemm_tc(w2, hidden_out, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets), len(tiles) + 2, tile_rows,
+                         y, paired=False)
+    ops().tc_status_check(DEV)
+    ref_y = np.stack([f64(hidden_out)[r] @ w2f[expert_of[r]].T for r in range(n)])
+    close(f64(y), ref_y, 2e-5, "tcgen05 down product")
+
+
+def test_gather_rows():
+    rng = np.random.default_rng(18)
+    x = dev(rng.normal(size=(20, 64)), torch.bfloat16)
+    rows = rng.integers(0, 20, size=37).astype(np.int32)
+    out = torch.empty(37, 64, dtype=torch.bfloat16, device=DEV)
+    ops().gather_rows(x, dev(rows), out)
+    assert torch.equal(out, x[torch.as_tensor(rows, device=DEV).long()])
