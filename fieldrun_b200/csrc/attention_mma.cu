@@ -46,11 +46,46 @@ __device__ __forceinline__ void tile_init(RowTile<HD>& st) {
     st.l[0] = st.l[1] = 0.f;
 }
 
-// Adds one page of 64 keys to the tile.  k_page: [64][HD]; vt_page: [HD][64]; key_base: position of the
-// page's first key; row r sees keys lo[r] <= j <= hi[r].  scale2 = softmax scale * log2(e).
+// Where a page's operands are read from: global memory (the page itself) ...
 template <int HD>
-__device__ __forceinline__ void tile_page(RowTile<HD>& st, const bf16* __restrict__ k_page, const bf16* __restrict__ vt_page,
-                                          int key_base, const int (&lo)[2], const int (&hi)[2], float scale2, int g, int t) {
+struct GlobalPage {
+    const bf16* k_page;      // [64][HD]
+    const bf16* vt_page;     // [HD][64]
+    // 8 dims 32 step + 8 t .. of key `key`
+    __device__ __forceinline__ uint4 k(int key, int step, int t) const {
+        return __ldg(reinterpret_cast<const uint4*>(k_page + (size_t)key * HD) + step * 4 + t);
+    }
+    // 8 keys 32 m + 8 t .. of dim `dim`
+    __device__ __forceinline__ uint4 v(int dim, int m, int t) const {
+        return __ldg(reinterpret_cast<const uint4*>(vt_page + (size_t)dim * FRB_PAGE) + m * 4 + t);
+    }
+};
+
+// ... or a copy of the page in shared memory, whose 16-byte chunks are swizzled so that the eight lanes of
+// a quarter warp (two rows, four chunks each) fall into different banks: chunk ^= (row & 1) << 2, for the
+// chunks that lie in whole groups of eight.
+template <int CHUNKS_PER_ROW>
+__device__ __forceinline__ int swizzled(int chunk, int row) {
+    return chunk < (CHUNKS_PER_ROW & ~7) ? chunk ^ ((row & 1) << 2) : chunk;
+}
+
+template <int HD>
+struct SharedPage {
+    const uint4* k_tile;     // [64][HD / 8] chunks
+    const uint4* vt_tile;    // [HD][8] chunks
+    __device__ __forceinline__ uint4 k(int key, int step, int t) const {
+        return k_tile[key * (HD / 8) + swizzled<HD / 8>(step * 4 + t, key)];
+    }
+    __device__ __forceinline__ uint4 v(int dim, int m, int t) const {
+        return vt_tile[dim * 8 + swizzled<8>(m * 4 + t, dim)];
+    }
+};
+
+// Adds one page of 64 keys to the tile.  key_base: position of the page's first key; row r sees keys
+// lo[r] <= j <= hi[r].  scale2 = softmax scale * log2(e).
+template <int HD, typename Page>
+__device__ __forceinline__ void tile_page(RowTile<HD>& st, const Page& page, int key_base, const int (&lo)[2],
+                                          const int (&hi)[2], float scale2, int g, int t) {
     float s[8][4];
     // scores: column block 4 m + u, column c = 2 t' + d of it stands for key 32 m + 8 t' + 2 u + d
 #pragma unroll
@@ -58,11 +93,10 @@ __device__ __forceinline__ void tile_page(RowTile<HD>& st, const bf16* __restric
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int key_local = 32 * m + 8 * (g >> 1) + 2 * u + (g & 1);
-            const uint4* kp = reinterpret_cast<const uint4*>(k_page + (size_t)key_local * HD) + t;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int step = 0; step < HD / 32; ++step) {
-                const uint4 kb = __ldg(kp + step * 4);
+                const uint4 kb = page.k(key_local, step, t);
                 mma_bf16(acc, st.q[step][0].x, st.q[step][1].x, st.q[step][0].y, st.q[step][1].y, kb.x, kb.y);
                 mma_bf16(acc, st.q[step][0].z, st.q[step][1].z, st.q[step][0].w, st.q[step][1].w, kb.z, kb.w);
             }
@@ -121,7 +155,7 @@ __device__ __forceinline__ void tile_page(RowTile<HD>& st, const bf16* __restric
         const uint32_t b2 = pack_bf16(s[4 * m + 3][0], s[4 * m + 3][1]), b3 = pack_bf16(s[4 * m + 3][2], s[4 * m + 3][3]);
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n) {
-            const uint4 vb = __ldg(reinterpret_cast<const uint4*>(vt_page + (size_t)(8 * n + g) * FRB_PAGE + 32 * m) + t);
+            const uint4 vb = page.v(8 * n + g, m, t);
             mma_bf16(st.o[n], a0, a1, a2, a3, vb.x, vb.y);
             mma_bf16(st.o[n], b0, b1, b2, b3, vb.z, vb.w);
         }
@@ -174,7 +208,8 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(DecodeAttnPar
         const int page = p.page_table[(size_t)p.seq_slot[b] * p.max_pages + page_index];
         const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
         const int lo[2] = {lo_key, lo_key}, hi[2] = {hi_key, hi_key};
-        tile_page(st, p.k_pages + at, p.v_pages + at, key_base, lo, hi, p.scale2, g, t);
+        const GlobalPage<HD> operands = {p.k_pages + at, p.v_pages + at};
+        tile_page(st, operands, key_base, lo, hi, p.scale2, g, t);
     }
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
@@ -268,10 +303,31 @@ struct PrefillAttnParams {
     int window, max_pages, num_heads, num_kv_heads;
 };
 
-// grid (tile of 16 queries, kv head); warps take the query heads of the group in turn, so the warps of a
-// block read the same keys and values at about the same time.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// Starts the copy of one page's keys and transposed values into a stage of shared memory (swizzled chunks).
+template <int HD>
+__device__ __forceinline__ void stage_page(uint4* k_tile, uint4* vt_tile, const bf16* __restrict__ k_page,
+                                           const bf16* __restrict__ vt_page) {
+    constexpr int CHUNKS = FRB_PAGE * HD / 8;           // 16-byte chunks of K, and as many of V
+    for (int c = threadIdx.x; c < CHUNKS; c += blockDim.x) {
+        const int key = c / (HD / 8), chunk = c % (HD / 8);
+        cp_async16(k_tile + key * (HD / 8) + swizzled<HD / 8>(chunk, key), reinterpret_cast<const uint4*>(k_page) + c);
+        const int dim = c >> 3, vchunk = c & 7;
+        cp_async16(vt_tile + dim * 8 + swizzled<8>(vchunk, dim), reinterpret_cast<const uint4*>(vt_page) + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// grid (tile of 16 queries, kv head).  The warps of a block take the query heads of the kv head's group:
+// they need the same keys and values, which the block copies page by page into two stages of shared memory
+// with cp.async, the next page on its way while the current one is multiplied.
 template <int HD>
 __global__ void __launch_bounds__(256) attention_prefill_mma_kernel(PrefillAttnParams p) {
+    extern __shared__ uint4 stages[];                   // 2 x (K tile, V^T tile), FRB_PAGE * HD / 8 chunks each
+    constexpr int TILE = FRB_PAGE * HD / 8;
     const int tile = blockIdx.x, kvh = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3;
     const int group = p.num_heads / p.num_kv_heads;
@@ -289,26 +345,46 @@ __global__ void __launch_bounds__(256) attention_prefill_mma_kernel(PrefillAttnP
     }
     const int last_key = start + min(q0 + 15, q_len - 1);
     const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
-    for (int hl = warp; hl < group; hl += nwarps) {
-        const int head = kvh * group + hl;
+    const int first_page = first_key / FRB_PAGE, last_page = last_key / FRB_PAGE;
+    for (int hbase = 0; hbase < group; hbase += nwarps) {
+        const int hl = hbase + warp;
+        const bool active = hl < group;
+        const int head = kvh * group + (active ? hl : 0);
         RowTile<HD> st;
         tile_init(st);
 #pragma unroll
         for (int r = 0; r < 2; ++r)
-            load_q_row(st, r, valid[r] ? p.q + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD : nullptr, t);
-        for (int page_index = first_key / FRB_PAGE; page_index <= last_key / FRB_PAGE; ++page_index) {
-            const int page = table[page_index];
-            const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
-            tile_page(st, p.k_pages + at, p.v_pages + at, page_index * FRB_PAGE, lo, hi, p.scale2, g, t);
+            load_q_row(st, r, (active && valid[r]) ? p.q + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD : nullptr, t);
+        {
+            const size_t at = ((size_t)table[first_page] * p.num_kv_heads + kvh) * FRB_PAGE * HD;
+            stage_page<HD>(stages, stages + TILE, p.k_pages + at, p.v_pages + at);
         }
+        for (int page_index = first_page; page_index <= last_page; ++page_index) {
+            const int cur = (page_index - first_page) & 1;
+            if (page_index < last_page) {
+                const size_t at = ((size_t)table[page_index + 1] * p.num_kv_heads + kvh) * FRB_PAGE * HD;
+                stage_page<HD>(stages + (cur ^ 1) * 2 * TILE, stages + (cur ^ 1) * 2 * TILE + TILE, p.k_pages + at, p.v_pages + at);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            if (active) {
+                const SharedPage<HD> page = {stages + cur * 2 * TILE, stages + cur * 2 * TILE + TILE};
+                tile_page(st, page, page_index * FRB_PAGE, lo, hi, p.scale2, g, t);
+            }
+            __syncthreads();                            // the stage is free for the page after the next
+        }
+        if (active) {
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            if (!valid[r]) continue;
-            const float inv = 1.0f / st.l[r];
-            bf16* dst = p.out + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD;
+            for (int r = 0; r < 2; ++r) {
+                if (!valid[r]) continue;
+                const float inv = 1.0f / st.l[r];
+                bf16* dst = p.out + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n)
-                *reinterpret_cast<uint32_t*>(dst + 8 * n + 2 * t) = pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+                for (int n = 0; n < HD / 8; ++n)
+                    *reinterpret_cast<uint32_t*>(dst + 8 * n + 2 * t) = pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+            }
         }
     }
 }
@@ -331,9 +407,12 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     dim3 grid(num_tiles, num_kv_heads);
-    if (head_dim == 32) attention_prefill_mma_kernel<32><<<grid, 32 * nwarps, 0, stream>>>(p);
-    else if (head_dim == 64) attention_prefill_mma_kernel<64><<<grid, 32 * nwarps, 0, stream>>>(p);
-    else if (head_dim == 96) attention_prefill_mma_kernel<96><<<grid, 32 * nwarps, 0, stream>>>(p);
-    else attention_prefill_mma_kernel<128><<<grid, 32 * nwarps, 0, stream>>>(p);
+    const size_t smem = (size_t)4 * FRB_PAGE * head_dim * sizeof(bf16);           // two stages of K and V^T
+#define LAUNCH(HD)                                                                                                  \
+    if (smem > 48 * 1024)                                                                                           \
+        cudaFuncSetAttribute(attention_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    attention_prefill_mma_kernel<HD><<<grid, 32 * nwarps, smem, stream>>>(p)
+    if (head_dim == 32) { LAUNCH(32); } else if (head_dim == 64) { LAUNCH(64); } else if (head_dim == 96) { LAUNCH(96); } else { LAUNCH(128); }
+#undef LAUNCH
     FRB_RETURN_LAUNCH("attention_prefill_mma");
 }

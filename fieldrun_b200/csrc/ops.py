@@ -113,10 +113,57 @@ def count_launches(n: int) -> None:
     _LAUNCHES += n
 
 
+_TIMINGS: Optional[list] = None
+
+
+def timing_start() -> None:
+    """Start recording a pair of CUDA events around every launch (kernels of this library and the library
+    products that go through :func:`timed`); :func:`timing_report` adds them up.  For finding out where a
+    step's time goes; it slows the host side down, so never inside a measurement."""
+    global _TIMINGS
+    _TIMINGS = []
+
+
+def timing_report() -> dict[str, tuple[int, float]]:
+    """name -> (launches, milliseconds) since :func:`timing_start`; stops recording."""
+    global _TIMINGS
+    torch.cuda.synchronize()
+    out: dict[str, tuple[int, float]] = {}
+    for name, begin, end in _TIMINGS or []:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + begin.elapsed_time(end))
+    _TIMINGS = None
+    return out
+
+
+class timed:
+    """``with timed("name"):`` records the enclosed launches under ``name`` while timing is on."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _TIMINGS is not None:
+            self.begin = torch.cuda.Event(enable_timing=True)
+            self.begin.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _TIMINGS is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            _TIMINGS.append((self.name, self.begin, end))
+        return False
+
+
 def _call(name: str, *args) -> None:
     global _LAUNCHES
     lib = library()
-    status = getattr(lib, name)(*args, _stream())
+    if _TIMINGS is not None:
+        with timed(name[4:]):
+            status = getattr(lib, name)(*args, _stream())
+    else:
+        status = getattr(lib, name)(*args, _stream())
     _LAUNCHES += _KERNELS_PER_CALL.get(name, 1)
     if status != 0:
         raise KernelError(f"{name}: {lib.frb_last_error().decode(errors='replace')} (status {status})")

@@ -49,9 +49,10 @@ def linear(rows: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]
     if rows.dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
             raise RuntimeError("a float32 matrix product was asked for while TF32 is allowed")
-        if out is None:
-            return torch.mm(rows, weight.t())
-        return torch.mm(rows, weight.t(), out=out)
+        with ops.timed(f"library_mm_f32[{weight.shape[0]}x{weight.shape[1]}]"):
+            if out is None:
+                return torch.mm(rows, weight.t())
+            return torch.mm(rows, weight.t(), out=out)
     count, inner = rows.shape
     features = weight.shape[0]
     if count <= STREAM_ROWS and inner % 32 == 0 and features % 16 == 0 and features <= STREAM_FEATURES \
@@ -64,7 +65,8 @@ def linear(rows: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]
         ops.expert_gemm_mma(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
                             tile_rows, result, paired=False, splits=ops.stream_splits(1, features, tile_rows))
         return result
-    result = torch.mm(rows, weight.t(), out_dtype=torch.float32)
+    with ops.timed(f"library_mm[{features}x{inner}]"):
+        result = torch.mm(rows, weight.t(), out_dtype=torch.float32)
     if out is None:
         return result
     out.copy_(result)
