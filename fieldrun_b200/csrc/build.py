@@ -32,7 +32,7 @@ def sources() -> list[str]:
 
 
 def _headers() -> list[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith(".cuh"))
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
 
 
 def _nvcc() -> str:
