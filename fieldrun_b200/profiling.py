@@ -1,0 +1,139 @@
+"""Small, self-contained workloads of the hot kernels at MiniMax-M2 layer sizes, for timing and for
+profilers.
+
+    python -m fieldrun_b200.profiling <case> [--launches N]
+
+Each case holds a few hundred MB on the device (more than the L2 cache, far less than a model), runs a few
+warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
+arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
+``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``.
+The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
+this library's own.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from .csrc import ops
+
+HIDDEN, WIDTH, HEADS, KV_HEADS, HEAD_DIM = 3072, 1536, 48, 8, 128
+
+
+def _time(launch, launches: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(launches):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / launches
+
+
+def _expert_lists(rows_per_expert: list[int], tile_rows: int, device):
+    offsets = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
+    tiles = [(e, offsets[e] + r) for e, n in enumerate(rows_per_expert) for r in range(0, n, tile_rows)]
+    as_dev = lambda a: torch.tensor(a, dtype=torch.int32, device=device)
+    return (as_dev([t[0] for t in tiles]), as_dev([t[1] for t in tiles]), as_dev([len(tiles)]), as_dev(offsets), len(tiles))
+
+
+def experts(kind: str, launches: int) -> dict:
+    dev = torch.device("cuda")
+    experts_n = 16
+    rows_per = [64] * experts_n if kind == "tc" else [1, 2] * (experts_n // 2)
+    tile_rows = 128 if kind == "tc" else 8
+    n = sum(rows_per)
+    w13 = (torch.randn(experts_n, 2 * WIDTH, HIDDEN, device=dev) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(experts_n, HIDDEN, WIDTH, device=dev) * 0.02).to(torch.bfloat16)
+    x = torch.randn(n, HIDDEN, device=dev).to(torch.bfloat16)
+    hidden = torch.empty(n, WIDTH, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(n, HIDDEN, dtype=torch.float32, device=dev)
+    tile_expert, tile_row0, num_tiles, offsets, tiles = _expert_lists(rows_per, tile_rows, dev)
+
+    def launch():
+        if kind == "tc":
+            ops.expert_gemm_tc(w13, x, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True)
+            ops.expert_gemm_tc(w2, hidden, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False)
+        else:
+            ops.expert_gemm_mma(w13, x, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True,
+                                splits=ops.stream_splits(tiles, WIDTH, tile_rows))
+            ops.expert_gemm_mma(w2, hidden, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False,
+                                splits=ops.stream_splits(tiles, HIDDEN, tile_rows))
+
+    ms = _time(launch, launches)
+    if kind == "tc":
+        ops.tc_status_check(dev)
+    weight_bytes = (w13.numel() + w2.numel()) * 2
+    flops = 2 * n * 3 * WIDTH * HIDDEN
+    return {"case": f"experts_{'tc' if kind == 'tc' else 'stream'}", "ms": round(ms, 4), "experts": experts_n, "rows": n,
+            "weight_gb_per_s": round(weight_bytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 2)}
+
+
+def attention(kind: str, launches: int) -> dict:
+    dev = torch.device("cuda")
+    batch, context = (8, 4096) if kind == "decode" else (1, 2048)
+    pages_per = context // 64
+    pages = batch * pages_per
+    keys = (torch.randn(pages, KV_HEADS, 64, HEAD_DIM, device=dev) * 0.3).to(torch.bfloat16)
+    values = (torch.randn(pages, KV_HEADS, HEAD_DIM, 64, device=dev) * 0.3).to(torch.bfloat16)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(batch, pages_per).contiguous()
+    slots = torch.arange(batch, dtype=torch.int32, device=dev)
+    scale = HEAD_DIM ** -0.5
+    if kind == "decode":
+        q = torch.randn(batch, HEADS * HEAD_DIM, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        positions = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+        chunks = context // ops.ATTENTION_CHUNK
+        part_o = torch.empty(batch, HEADS, chunks, HEAD_DIM, dtype=torch.float32, device=dev)
+        part_ml = torch.empty(batch, HEADS, chunks, 2, dtype=torch.float32, device=dev)
+        launch = lambda: ops.attention_decode_mma(q, keys, values, table, positions, slots, part_o, part_ml, out, num_heads=HEADS,
+                                                  num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None,
+                                                  max_chunks=chunks)
+        ms = _time(launch, launches)
+        kv_bytes = (keys.numel() + values.numel()) * 2
+        return {"case": "attention_decode", "ms": round(ms, 4), "batch": batch, "context": context,
+                "kv_gb_per_s": round(kv_bytes / ms / 1e6, 1)}
+    q = torch.randn(context, HEADS * HEAD_DIM, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    tiles = context // 16
+    tile_seq = torch.zeros(tiles, dtype=torch.int32, device=dev)
+    tile_q0 = torch.arange(0, context, 16, dtype=torch.int32, device=dev)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    q_len = torch.tensor([context], dtype=torch.int32, device=dev)
+    cu = torch.tensor([0, context], dtype=torch.int32, device=dev)
+    launch = lambda: ops.attention_prefill_mma(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
+                                               num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None)
+    ms = _time(launch, launches)
+    flops = 4 * HEADS * HEAD_DIM * context * (context + 1) // 2
+    return {"case": "attention_prefill", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
+
+
+CASES = {
+    "experts_tc": lambda n: experts("tc", n),
+    "experts_stream": lambda n: experts("stream", n),
+    "attention_decode": lambda n: attention("decode", n),
+    "attention_prefill": lambda n: attention("prefill", n),
+}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("case", choices=sorted(CASES) + ["all"])
+    parser.add_argument("--launches", type=int, default=5)
+    args = parser.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("fieldrun_b200.profiling needs a CUDA device")
+    torch.manual_seed(0)
+    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+        print(json.dumps(CASES[name](args.launches)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
