@@ -3,7 +3,7 @@ profilers.
 
     python -m fieldrun_b200.profiling <case> [--launches N]
 
-Each case holds a few hundred MB on the device (more than the L2 cache, far less than a model), runs a few
+Each case holds between a few hundred MB and 2 GB on the device (more than the L2 cache, far less than a model), runs a few
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
 arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
 ``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``.
@@ -45,7 +45,7 @@ def _expert_lists(rows_per_expert: list[int], tile_rows: int, device):
 
 def experts(kind: str, launches: int) -> dict:
     dev = torch.device("cuda")
-    experts_n = 16
+    experts_n = 64
     rows_per = [64] * experts_n if kind == "tc" else [1, 2] * (experts_n // 2)
     tile_rows = 128 if kind == "tc" else 8
     n = sum(rows_per)
