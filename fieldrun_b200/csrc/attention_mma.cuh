@@ -188,9 +188,12 @@ struct DecodeAttnParams {
 };
 
 // grid (chunk, kv head, sequence), 4 warps.  Rows of the tile are the query heads of the kv head's group.
+// Each warp takes one page of the chunk: scores, softmax within the page, then P V in two halves of the
+// head size so that few accumulators are alive at a time (more blocks per SM, more loads in flight); the
+// four warps' results are combined through shared memory.
 template <int HD>
-__global__ void __launch_bounds__(128) attention_decode_mma_kernel(DecodeAttnParams p) {
-    __shared__ float sm_o[4][16][HD + 4];
+__global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttnParams p) {
+    __shared__ float sm_o[4][16][HD + 8];
     __shared__ float sm_m[4][16], sm_l[4][16];
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -199,30 +202,98 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(DecodeAttnPar
     const int hi_key = pos, lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     if (chunk * ATT_CHUNK > hi_key || (chunk + 1) * ATT_CHUNK <= lo_key) return;      // the merge skips these chunks
 
-    RowTile<HD> st;
-    tile_init(st);
     const int page_index = chunk * (ATT_CHUNK / FRB_PAGE) + warp;
     const int key_base = page_index * FRB_PAGE;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
     if (key_base <= hi_key && key_base + FRB_PAGE > lo_key) {
-        const bf16* q_base = p.q + ((size_t)b * p.num_heads + (size_t)kvh * group) * HD;
-        load_q_row(st, 0, g < group ? q_base + (size_t)g * HD : nullptr, t);
-        load_q_row(st, 1, g + 8 < group ? q_base + (size_t)(g + 8) * HD : nullptr, t);
         const int page = p.page_table[(size_t)p.seq_slot[b] * p.max_pages + page_index];
         const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
-        const int lo[2] = {lo_key, lo_key}, hi[2] = {hi_key, hi_key};
         const GlobalPage<HD> operands = {p.k_pages + at, p.v_pages + at};
-        tile_page(st, operands, key_base, lo, hi, p.scale2, g, t);
-    }
+        float s[8][4];
+        {
+            const bf16* q_base = p.q + ((size_t)b * p.num_heads + (size_t)kvh * group) * HD;
+            const bf16* q0 = g < group ? q_base + (size_t)g * HD : nullptr;
+            const bf16* q1 = g + 8 < group ? q_base + (size_t)(g + 8) * HD : nullptr;
+            uint4 q[HD / 32][2];
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-        sm_o[warp][g][8 * n + 2 * t] = st.o[n][0];
-        sm_o[warp][g][8 * n + 2 * t + 1] = st.o[n][1];
-        sm_o[warp][g + 8][8 * n + 2 * t] = st.o[n][2];
-        sm_o[warp][g + 8][8 * n + 2 * t + 1] = st.o[n][3];
+            for (int step = 0; step < HD / 32; ++step) {
+                q[step][0] = q0 ? __ldg(reinterpret_cast<const uint4*>(q0 + 32 * step) + t) : make_uint4(0, 0, 0, 0);
+                q[step][1] = q1 ? __ldg(reinterpret_cast<const uint4*>(q1 + 32 * step) + t) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int key_local = 32 * m + 8 * (g >> 1) + 2 * u + (g & 1);
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int step = 0; step < HD / 32; ++step) {
+                        const uint4 kb = operands.k(key_local, step, t);
+                        mma_bf16(acc, q[step][0].x, q[step][1].x, q[step][0].y, q[step][1].y, kb.x, kb.y);
+                        mma_bf16(acc, q[step][0].z, q[step][1].z, q[step][0].w, q[step][1].w, kb.z, kb.w);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
+                        const float v = (key >= lo_key && key <= hi_key) ? acc[e] * p.scale2 : -INFINITY;
+                        s[4 * m + u][e] = v;
+                        row_max[e >> 1] = fmaxf(row_max[e >> 1], v);
+                    }
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
+            row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
+        }
+        // the page holds at least one visible key, and every row sees the same keys: the maxima are finite
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[j][e] - row_max[e >> 1]);
+                s[j][e] = pv;
+                row_sum[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+        }
+        uint32_t pa[2][4], pb[2][4];
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            pa[m][0] = pack_bf16(s[4 * m][0], s[4 * m][1]);         pa[m][1] = pack_bf16(s[4 * m][2], s[4 * m][3]);
+            pa[m][2] = pack_bf16(s[4 * m + 1][0], s[4 * m + 1][1]); pa[m][3] = pack_bf16(s[4 * m + 1][2], s[4 * m + 1][3]);
+            pb[m][0] = pack_bf16(s[4 * m + 2][0], s[4 * m + 2][1]); pb[m][1] = pack_bf16(s[4 * m + 2][2], s[4 * m + 2][3]);
+            pb[m][2] = pack_bf16(s[4 * m + 3][0], s[4 * m + 3][1]); pb[m][3] = pack_bf16(s[4 * m + 3][2], s[4 * m + 3][3]);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float o[HD / 16][4];
+#pragma unroll
+            for (int n = 0; n < HD / 16; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int n = 0; n < HD / 16; ++n) {
+                    const uint4 vb = operands.v(8 * (half * (HD / 16) + n) + g, m, t);
+                    mma_bf16(o[n], pa[m][0], pa[m][1], pa[m][2], pa[m][3], vb.x, vb.y);
+                    mma_bf16(o[n], pb[m][0], pb[m][1], pb[m][2], pb[m][3], vb.z, vb.w);
+                }
+#pragma unroll
+            for (int n = 0; n < HD / 16; ++n) {
+                const int d = 8 * (half * (HD / 16) + n) + 2 * t;
+                *reinterpret_cast<float2*>(&sm_o[warp][g][d]) = make_float2(o[n][0], o[n][1]);
+                *reinterpret_cast<float2*>(&sm_o[warp][g + 8][d]) = make_float2(o[n][2], o[n][3]);
+            }
+        }
     }
     if (t == 0) {
-        sm_m[warp][g] = st.m[0]; sm_l[warp][g] = st.l[0];
-        sm_m[warp][g + 8] = st.m[1]; sm_l[warp][g + 8] = st.l[1];
+        sm_m[warp][g] = row_max[0]; sm_l[warp][g] = row_sum[0];
+        sm_m[warp][g + 8] = row_max[1]; sm_l[warp][g + 8] = row_sum[1];
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < group * HD; idx += 128) {
@@ -233,9 +304,11 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(DecodeAttnPar
         float sum = 0.f, acc = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(sm_m[w][r] - top);        // a warp without visible keys has m = -inf: f = 0
-            sum += sm_l[w][r] * f;
-            acc += sm_o[w][r][d] * f;
+            if (sm_l[w][r] > 0.f) {                             // a warp whose page holds no visible key wrote nothing
+                const float f = exp2f(sm_m[w][r] - top);
+                sum += sm_l[w][r] * f;
+                acc += sm_o[w][r][d] * f;
+            }
         }
         const size_t row = ((size_t)b * p.num_heads + (size_t)kvh * group + r) * p.max_chunks + chunk;
         p.part_o[row * HD + d] = acc;

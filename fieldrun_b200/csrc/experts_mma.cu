@@ -27,25 +27,26 @@ __device__ __forceinline__ uint4 load_stream(const void* ptr) {
     return v;
 }
 
-#define EM_GROUPS 4          // groups of 16 features per block; a block has EM_GROUPS * splits warps
+#define EM_MAX_GROUPS 4      // groups of 16 features per block: 1, 2 or 4; a block has groups * splits warps
 
 // grid (row tile, block of 64 features).  NB column blocks of 8 rows each: the tile has at most 8 NB rows.
 // The block's warps are (feature group, k split): with few tiles (a batch of one, or a dense layer as a
-// single "expert") the inner dimension is cut into blockDim / 128 parts, so that enough loads are in
-// flight; the parts are added in the order of k, by the warps of the first part, through shared memory.
+// single "expert") a block takes fewer feature groups and the inner dimension is cut into parts, so that
+// there are enough blocks for every SM and enough loads in flight; the parts are added in the order of k,
+// by the warps of the first part, through shared memory.
 template <int NB, bool PAIRED, typename OutT>
 __global__ void __launch_bounds__(512 / NB)
 expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, const int* __restrict__ x_rows,
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out, int F, int K,
-                       int k_per_split) {
-    extern __shared__ float partial[];       // [splits - 1][EM_GROUPS][NACC][32]
+                       int k_per_split, int groups) {
+    extern __shared__ float partial[];       // [splits - 1][groups][NACC][32]
     constexpr int NACC = NB * 4 * (PAIRED ? 2 : 1);
     const int tile = blockIdx.x;
     if (tile >= num_tiles[0]) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int group = warp & (EM_GROUPS - 1), split = warp / EM_GROUPS, splits = blockDim.x / (32 * EM_GROUPS);
-    const int f0 = (blockIdx.y * EM_GROUPS + group) * 16;
+    const int group = warp % groups, split = warp / groups, splits = blockDim.x / (32 * groups);
+    const int f0 = (blockIdx.y * groups + group) * 16;
     const bool active = f0 < F;
     const int e = tile_expert[tile];
     const int row0 = tile_row0[tile];
@@ -103,7 +104,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
     }
     if (splits > 1) {
         if (split > 0) {
-            float* mine = partial + ((size_t)(split - 1) * EM_GROUPS + group) * NACC * 32 + lane;
+            float* mine = partial + ((size_t)(split - 1) * groups + group) * NACC * 32 + lane;
 #pragma unroll
             for (int j = 0; j < NB; ++j)
 #pragma unroll
@@ -115,7 +116,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
         __syncthreads();
         if (split > 0) return;
         for (int s = 1; s < splits; ++s) {
-            const float* theirs = partial + ((size_t)(s - 1) * EM_GROUPS + group) * NACC * 32 + lane;
+            const float* theirs = partial + ((size_t)(s - 1) * groups + group) * NACC * 32 + lane;
 #pragma unroll
             for (int j = 0; j < NB; ++j)
 #pragma unroll
@@ -143,29 +144,31 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
 
 // W bf16 [E][(paired ? 2 : 1) F][K]; X bf16 rows of K; tiles of at most tile_rows (8, 16 or 32) rows.
 // paired: out bf16 [N, F] = silu(x W1^T) * (x W3^T); else out float32 [N, F] = x W^T.
-// splits: parts the inner size is cut into within a block (1 when there are many tiles).
+// splits: parts the inner size is cut into within a block (1 when there are many tiles); groups: groups of
+// 16 features a block takes (4 when there are many tiles).
 FRB_API int frb_expert_gemm_mma(const void* W, const void* X, const int* x_rows, const int* tile_expert, const int* tile_row0,
                                 const int* num_tiles, const int* offsets, int max_tiles, int tile_rows, void* out, int F, int K,
-                                int paired, int splits, cudaStream_t stream) {
+                                int paired, int splits, int groups, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     FRB_CHECK_ARG(K % 32 == 0 && K > 0, "expert stream: inner size %d is not a multiple of 32", K);
     FRB_CHECK_ARG(F % 16 == 0 && F > 0, "expert stream: %d features are not a multiple of 16", F);
     FRB_CHECK_ARG(tile_rows == 8 || tile_rows == 16 || tile_rows == 32, "expert stream: tiles of %d rows", tile_rows);
     const int nb = tile_rows / 8;
-    FRB_CHECK_ARG(splits >= 1 && splits * nb <= 4, "expert stream: %d splits of the inner size with tiles of %d rows", splits,
-                  tile_rows);
+    FRB_CHECK_ARG(groups == 1 || groups == 2 || groups == 4, "expert stream: %d feature groups per block", groups);
+    FRB_CHECK_ARG(splits >= 1 && splits * groups * nb <= 16, "expert stream: %d splits x %d groups with tiles of %d rows exceed a block",
+                  splits, groups, tile_rows);
     const int k_per_split = ((K + splits - 1) / splits + 127) / 128 * 128;
-    dim3 grid(max_tiles, (F + 16 * EM_GROUPS - 1) / (16 * EM_GROUPS));
+    dim3 grid(max_tiles, (F + 16 * groups - 1) / (16 * groups));
     FRB_CHECK_ARG(grid.y <= 65535, "expert stream: %d features exceed the grid", F);
-    const int threads = 32 * EM_GROUPS * splits;
-    const size_t smem = (size_t)(splits - 1) * EM_GROUPS * nb * 4 * (paired ? 2 : 1) * 32 * sizeof(float);
+    const int threads = 32 * groups * splits;
+    const size_t smem = (size_t)(splits - 1) * groups * nb * 4 * (paired ? 2 : 1) * 32 * sizeof(float);
 #define LAUNCH(NB)                                                                                                        \
     if (paired)                                                                                                           \
         expert_gemm_mma_kernel<NB, true, bf16><<<grid, threads, smem, stream>>>(                                          \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split); \
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split, groups); \
     else                                                                                                                  \
         expert_gemm_mma_kernel<NB, false, float><<<grid, threads, smem, stream>>>(                                        \
-            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split)
+            (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split, groups)
     if (tile_rows == 8) { LAUNCH(1); } else if (tile_rows == 16) { LAUNCH(2); } else { LAUNCH(4); }
 #undef LAUNCH
     FRB_RETURN_LAUNCH("expert_gemm_mma");

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifii",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
-    "frb_expert_gemm_mma": "pppppppiipiiii",
+    "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_expert_gemm_tc": "pipippppiipiiip",
     "frb_gather_rows_bf16": "pppii",
@@ -328,15 +328,15 @@ def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 
 def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
                     tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
-                    tile_rows: int, out: torch.Tensor, *, paired: bool, splits: int = 1) -> None:
-    """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows; ``splits`` parts of
-    the inner size per block, splits * tile_rows <= 32)."""
+                    tile_rows: int, out: torch.Tensor, *, paired: bool, splits: int = 1, groups: int = 4) -> None:
+    """The expert products as a stream over bfloat16 weights (tiles of 8, 16 or 32 rows; per block ``groups``
+    groups of 16 features and ``splits`` parts of the inner size; see :func:`stream_shape`)."""
     _want(w, torch.bfloat16, "streamed expert weights")
     _want(x, torch.bfloat16, "streamed expert inputs")
     _want(out, torch.bfloat16 if paired else torch.float32, "streamed expert outputs")
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_mma", _ptr(w), _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
-          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits))
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits), int(groups))
 
 
 SMALL_ROUTE_ASSIGNMENTS = 1024
@@ -354,10 +354,16 @@ def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: 
           _ptr(tile_row0), _ptr(num_tiles))
 
 
-def stream_splits(tiles: int, features: int, tile_rows: int) -> int:
-    """Parts to cut the inner size into so that about 2048 warps stream weights (see the kernel's note)."""
-    groups = max(1, tiles * ((features + 15) // 16))
-    return max(1, min(4 // (tile_rows // 8), -(-2048 // groups)))
+def stream_shape(tiles: int, features: int, inner: int, tile_rows: int) -> dict:
+    """How a block of the streaming kernel is cut: with many tiles 4 groups of 16 features and the whole
+    inner size; with few tiles fewer groups per block (more blocks, about two per SM or more) and the inner
+    size in parts (about 2048 warps streaming).  Returns the keyword arguments ``splits`` and ``groups``."""
+    nb = tile_rows // 8
+    total = max(1, tiles * ((features + 15) // 16))
+    groups = 4 if total >= 4 * 296 else 2 if total >= 2 * 296 else 1
+    most = max(1, 16 // (nb * groups))
+    splits = max(1, min(most, -(-2048 // total), max(1, inner // 256)))
+    return {"splits": splits, "groups": groups}
 
 
 _TC_STATUS: dict[str, torch.Tensor] = {}

@@ -143,10 +143,10 @@ class RoutedExperts(FeedForward):
             tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
             ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
                                 p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True,
-                                splits=ops.stream_splits(tiles, self.expert_width, p["tile_rows"]))
+                                **ops.stream_shape(tiles, self.expert_width, self.hidden_size, p["tile_rows"]))
             ops.expert_gemm_mma(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                 p["max_tiles"], p["tile_rows"], y, paired=False,
-                                splits=ops.stream_splits(tiles, self.hidden_size, p["tile_rows"]))
+                                **ops.stream_shape(tiles, self.hidden_size, self.expert_width, p["tile_rows"]))
             return y
         ops.expert_gemm_generic(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
                                 p["offsets"], p["max_tiles"], hidden, paired=True)

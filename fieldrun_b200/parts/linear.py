@@ -63,7 +63,7 @@ def linear(rows: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]
         tile_expert, tile_row0, num_tiles, offsets = _one_tile(rows.device, count)
         result = out if out is not None else torch.empty((count, features), dtype=torch.float32, device=rows.device)
         ops.expert_gemm_mma(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
-                            tile_rows, result, paired=False, splits=ops.stream_splits(1, features, tile_rows))
+                            tile_rows, result, paired=False, **ops.stream_shape(1, features, inner, tile_rows))
         return result
     with ops.timed(f"library_mm[{features}x{inner}]"):
         result = torch.mm(rows, weight.t(), out_dtype=torch.float32)

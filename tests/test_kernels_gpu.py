@@ -522,8 +522,8 @@ def test_choice_and_lists_in_one_launch_equal_the_separate_kernels(tokens, top_k
         assert torch.equal(a[name][:nt], b[name][:nt]), name
 
 
-@pytest.mark.parametrize("tile_rows,splits", [(8, 2), (8, 4), (16, 2)])
-def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits):
+@pytest.mark.parametrize("tile_rows,splits,groups", [(8, 2, 4), (8, 4, 4), (16, 2, 4), (8, 8, 2), (8, 16, 1), (32, 2, 2), (16, 1, 1)])
+def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits, groups):
     rng = np.random.default_rng(16)
     experts, width, hidden, rows_per = 3, 96, 3072, [1, 0, tile_rows]
     w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.05, torch.bfloat16)
@@ -533,10 +533,10 @@ def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits):
     sorted_token = rng.integers(0, 9, size=n).astype(np.int32)
     tile_expert, tile_row0, num_tiles = np.array([0, 2], dtype=np.int32), np.array([0, 1], dtype=np.int32), np.array([2], dtype=np.int32)
     outs = []
-    for s in (1, splits):
+    for s, g in ((1, 4), (splits, groups)):
         out = torch.full((n, width), 9.0, dtype=torch.bfloat16, device=DEV)
         ops().expert_gemm_mma(w13, x, dev(sorted_token), dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets), 2,
-                              tile_rows, out, paired=True, splits=s)
+                              tile_rows, out, paired=True, splits=s, groups=g)
         outs.append(f64(out))
     xs, wf = f64(x), f64(w13)
     expert_of = np.repeat(np.arange(experts), rows_per)
@@ -544,6 +544,7 @@ def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits):
                     for r in range(n)])
     close(outs[0], ref, 1e-2, "one part")
     close(outs[1], ref, 1e-2, f"{splits} parts")
+    n = min(n, 32)                                            # one tile holds at most 32 rows
     y = torch.empty(n, 80, dtype=torch.float32, device=DEV)
     w = dev(rng.normal(size=(1, 80, hidden)) * 0.05, torch.bfloat16)
     one = dev(np.array([0], dtype=np.int32))
