@@ -49,25 +49,51 @@ FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype
 // ----------------------------------------------------------------------------- RMSNorm (+ residual add)
 
 #define NORM_BLOCK 1024
+#define NORM_MAX_TOP_K 32
 
-// One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]); if write_back the
-// sum is stored to x[src] (the residual stream).  out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and,
-// when out32 is given, in float32 as well.
+// The update of the residual stream may come as the outputs of a token's experts, not yet summed:
+// update[src] = sum over ranks r, in rank order, of weights[src, r] * y[row_of_assign[src * k + r]]
+// (src/minimax.rs:121-123).
+struct ExpertSum {
+    const float* y;               // [N, width], null: none
+    const float* weights;         // [T, k]
+    const int* row_of_assign;     // [T * k]
+    int top_k;
+};
+
+// One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]) (+ the experts' sum of
+// src); if write_back the sum is stored to x[src] (the residual stream).
+// out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and, when out32 is given, in float32 as well.
 template <typename OutT, typename WT>
 __global__ void __launch_bounds__(NORM_BLOCK)
-rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const int* __restrict__ rows,
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum experts, const int* __restrict__ rows,
                const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
                int write_back) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
+    __shared__ float expert_weight[NORM_MAX_TOP_K];
+    __shared__ const float* expert_row[NORM_MAX_TOP_K];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * width;
     const float* dr = delta ? delta + (size_t)src * width : nullptr;
+    if (experts.y) {                       // the token's weights and rows first, so that the loads below do not wait in turn
+        if (threadIdx.x < experts.top_k) {
+            const int at = src * experts.top_k + threadIdx.x;
+            expert_weight[threadIdx.x] = experts.weights[at];
+            expert_row[threadIdx.x] = experts.y + (size_t)experts.row_of_assign[at] * width;
+        }
+        __syncthreads();
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
         float v = xr[i];
         if (dr) v += dr[i];
+        if (experts.y) {
+            float sum = 0.f;
+            for (int k = 0; k < experts.top_k; ++k) sum += expert_weight[k] * expert_row[k][i];
+            v += sum;
+        }
         row[i] = v;
         ss += v * v;
         if (write_back) xr[i] = v;
@@ -81,16 +107,20 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const int
     }
 }
 
-FRB_API int frb_rmsnorm(float* x, const float* delta, const int* rows, const void* weight, int weight_dtype,
+FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, const float* expert_weights,
+                        const int* row_of_assign, int top_k, const int* rows, const void* weight, int weight_dtype,
                         float eps, int num_rows, int width, void* out, int out_dtype, float* out32,
                         int write_back, cudaStream_t stream) {
     if (num_rows == 0) return 0;
+    FRB_CHECK_ARG(expert_y == nullptr || (top_k >= 1 && top_k <= NORM_MAX_TOP_K), "rmsnorm: %d experts per token exceed %d",
+                  top_k, NORM_MAX_TOP_K);
+    ExpertSum experts = {expert_y, expert_weights, row_of_assign, top_k};
     const size_t smem = (size_t)width * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "rmsnorm: width %d needs %zu bytes of shared memory, more than 200 KB", width, smem);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
         auto kernel = rmsnorm_kernel<OutT, WT>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<num_rows, NORM_BLOCK, smem, stream>>>(x, delta, rows, (const WT*)weight, eps, width, (OutT*)out,
+        kernel<<<num_rows, NORM_BLOCK, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out,
                                                        out32, write_back);
     }));
     FRB_RETURN_LAUNCH("rmsnorm");

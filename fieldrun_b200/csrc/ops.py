@@ -21,7 +21,7 @@ _P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlon
 # entry point -> argument types ('p' pointer, 'i' int, 'f' float, 'l' long long); the stream is appended
 _SIGNATURES = {
     "frb_embed_rows": "ppipiii",
-    "frb_rmsnorm": "ppppifiipipi",
+    "frb_rmsnorm": "pppppippifiipipi",
     "frb_qkv_prepare": "pippifppipppipppiiiiiiii",
     "frb_add_rows": "ppl",
     "frb_attention_generic": "pppipipppiiiifi",
@@ -35,6 +35,7 @@ _SIGNATURES = {
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
+    "frb_router_small": "ppipppiiiifipppppppp",
     "frb_expert_gemm_tc": "pipippppiipiiip",
     "frb_gather_rows_bf16": "pppii",
 }
@@ -186,9 +187,11 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-            out32: Optional[torch.Tensor] = None, write_back: bool = False) -> None:
+            out32: Optional[torch.Tensor] = None, write_back: bool = False,
+            experts: Optional[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> None:
     """out[r] = rmsnorm(x[src] + delta[src]) * weight with src = rows[r] (or r); the sum is stored back
-    into x when write_back."""
+    into x when write_back.  ``experts`` = (y [N, width], weights [T, k], row_of_assign [T * k]) adds the
+    weighted sum of each token's expert outputs, in rank order, as a further update."""
     _want(x, torch.float32, "the residual stream")
     if delta is not None:
         _want(delta, torch.float32, "the residual update")
@@ -198,8 +201,16 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         _want(out32, torch.float32, "the 32-bit copy")
     num_rows = rows.numel() if rows is not None else x.shape[0]
     width = x.shape[-1]
-    _call("frb_rmsnorm", _ptr(x), _ptr(delta), _ptr(rows), _ptr(weight), _code(weight.dtype), float(eps), num_rows, width,
-          _ptr(out), _code(out.dtype), _ptr(out32), int(write_back))
+    y = ew = rowmap = None
+    top_k = 0
+    if experts is not None:
+        y, ew, rowmap = experts
+        _want(y, torch.float32, "expert outputs")
+        _want(ew, torch.float32, "expert weights")
+        _want(rowmap, torch.int32, "rows of the assignments")
+        top_k = ew.shape[-1]
+    _call("frb_rmsnorm", _ptr(x), _ptr(delta), _ptr(y), _ptr(ew), _ptr(rowmap), top_k, _ptr(rows), _ptr(weight),
+          _code(weight.dtype), float(eps), num_rows, width, _ptr(out), _code(out.dtype), _ptr(out32), int(write_back))
 
 
 def add_rows(x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -340,6 +351,7 @@ def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Ten
 
 
 SMALL_ROUTE_ASSIGNMENTS = 1024
+ROUTER_SMALL_TOKENS = 8       # most tokens of a step for router_small
 
 
 def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,
@@ -408,3 +420,24 @@ def expert_gemm_tc(w: torch.Tensor, x: torch.Tensor, tile_expert: torch.Tensor, 
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_tc", _ptr(w), w.shape[0], _ptr(x), x.shape[0], _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
           _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), _ptr(tc_status(w.device)))
+
+
+_ROUTER_TICKETS: dict[str, torch.Tensor] = {}
+
+
+def router_small(act32: torch.Tensor, router: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
+                 renormalize: bool, routed_scale: float, tile_rows: int, ids: torch.Tensor, weights: torch.Tensor,
+                 offsets: torch.Tensor, sorted_token: torch.Tensor, row_of_assign: torch.Tensor, tile_expert: torch.Tensor,
+                 tile_row0: torch.Tensor, num_tiles: torch.Tensor) -> None:
+    """Router logits (float32 rows x float32 weight), expert choice and expert-sorted lists in one launch, for
+    steps of at most 1024 (token, expert) pairs."""
+    _want(act32, torch.float32, "router input")
+    _want(router, torch.float32, "router weight")
+    _want(logits, torch.float32, "router logits")
+    tokens, width = act32.shape
+    key = str(act32.device)
+    if key not in _ROUTER_TICKETS:
+        _ROUTER_TICKETS[key] = torch.zeros(1, dtype=torch.int32, device=act32.device)
+    _call("frb_router_small", _ptr(act32), _ptr(router), width, _ptr(logits), _ptr(_ROUTER_TICKETS[key]), _ptr(bias), tokens,
+          router.shape[0], top_k, int(renormalize), float(routed_scale), tile_rows, _ptr(ids), _ptr(weights), _ptr(offsets),
+          _ptr(sorted_token), _ptr(row_of_assign), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles))

@@ -14,7 +14,7 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
                                              int top_k, int renormalize, float routed_scale, float* score, float* choice,
                                              int* __restrict__ ids, float* __restrict__ weights, int lane) {
     for (int e = lane; e < num_experts; e += 32) {
-        const float s = 1.0f / (1.0f + expf(-z[e]));
+        const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));      // read through L2: another block may have written it
         score[e] = s;
         choice[e] = bias ? s + bias[e] : s;
     }
@@ -180,28 +180,39 @@ FRB_API int frb_expert_plan(const int* ids, int num_tokens, int top_k, int num_e
 
 // For steps of few tokens (T * k <= 1024): one block picks every token's experts (a warp per token, in
 // turn), then sorts the assignments by expert and writes the same lists as the three kernels above.
-__global__ void __launch_bounds__(SMALL_WARPS * 32)
-route_plan_small_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_tokens, int num_experts,
-                        int top_k, int renormalize, float routed_scale, int tile_rows, int* __restrict__ ids,
-                        float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ sorted_token,
-                        int* __restrict__ row_of_assign, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                        int* __restrict__ num_tiles) {
-    extern __shared__ float sm[];
-    __shared__ int s_ids[SMALL_MAX_ASSIGN];
+struct SmallRouteParams {
+    const float* logits;     // [T, E]
+    const float* bias;       // [E] or null
+    int num_tokens, num_experts, top_k, renormalize;
+    float routed_scale;
+    int tile_rows;
+    int* ids;                // [T, k]
+    float* weights;          // [T, k]
+    int* offsets;            // [E + 1]
+    int* sorted_token;       // [N]
+    int* row_of_assign;      // [N]
+    int* tile_expert;
+    int* tile_row0;
+    int* num_tiles;
+};
+
+// The work of one block of SMALL_WARPS warps: every token's choice, then the lists.  sm: dynamic shared memory.
+__device__ __forceinline__ void route_and_plan(const SmallRouteParams& p, float* sm, int* s_ids) {
+    const int num_experts = p.num_experts, top_k = p.top_k, tile_rows = p.tile_rows;
     float* scratch = sm;                                                 // [SMALL_WARPS][2][E]
     int* count = reinterpret_cast<int*>(sm + (size_t)SMALL_WARPS * 2 * num_experts);   // [E]
     int* first = count + num_experts;                                    // [E + 1]
     int* first_tile = first + num_experts + 1;                           // [E + 1]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int num_assign = num_tokens * top_k;
-    for (int t = warp; t < num_tokens; t += SMALL_WARPS)
-        pick_experts(logits + (size_t)t * num_experts, bias, num_experts, top_k, renormalize, routed_scale,
+    const int num_assign = p.num_tokens * top_k;
+    for (int t = warp; t < p.num_tokens; t += SMALL_WARPS)
+        pick_experts(p.logits + (size_t)t * num_experts, p.bias, num_experts, top_k, p.renormalize, p.routed_scale,
                      scratch + (size_t)warp * 2 * num_experts, scratch + (size_t)warp * 2 * num_experts + num_experts,
-                     ids + (size_t)t * top_k, weights + (size_t)t * top_k, lane);
+                     p.ids + (size_t)t * top_k, p.weights + (size_t)t * top_k, lane);
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int a = threadIdx.x; a < num_assign; a += blockDim.x) {
-        const int e = ids[a];                                            // written by this block, above
+        const int e = p.ids[a];                                          // written by this block, above
         s_ids[a] = e;
         atomicAdd(&count[e], 1);
     }
@@ -226,22 +237,22 @@ route_plan_small_kernel(const float* __restrict__ logits, const float* __restric
             rows_before += count[e];
             tiles_before += (count[e] + tile_rows - 1) / tile_rows;
         }
-        if (lane == 0) { first[num_experts] = total_rows; num_tiles[0] = total_tiles; }
+        if (lane == 0) { first[num_experts] = total_rows; p.num_tiles[0] = total_tiles; }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) offsets[e] = first[e];
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) p.offsets[e] = first[e];
     for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
         int tile = first_tile[e];
         for (int r = 0; r < count[e]; r += tile_rows, ++tile) {
-            tile_expert[tile] = e;
-            tile_row0[tile] = first[e] + r;
+            p.tile_expert[tile] = e;
+            p.tile_row0[tile] = first[e] + r;
         }
         int at = first[e];
         if (count[e] > 0) {
             for (int a = 0; a < num_assign; ++a) {
                 if (s_ids[a] == e) {
-                    sorted_token[at] = a / top_k;
-                    row_of_assign[a] = at;
+                    p.sorted_token[at] = a / top_k;
+                    p.row_of_assign[a] = at;
                     ++at;
                 }
             }
@@ -249,23 +260,129 @@ route_plan_small_kernel(const float* __restrict__ logits, const float* __restric
     }
 }
 
-// logits [T, E] -> ids, weights and the expert-sorted lists, for T * k <= 1024, in one launch.
+__global__ void __launch_bounds__(SMALL_WARPS * 32) route_plan_small_kernel(SmallRouteParams p) {
+    extern __shared__ float sm[];
+    __shared__ int s_ids[SMALL_MAX_ASSIGN];
+    route_and_plan(p, sm, s_ids);
+}
+
+#define ROUTER_SMALL_TOKENS 8       // most tokens of a step that the one-launch router takes
+#define ROUTER_SMALL_EXPERTS 2      // experts per block: SMALL_WARPS / 2 warps share one expert's inner size
+
+// Router logits and everything after them in one launch, for steps of at most 8 tokens.  A block computes
+// the logits of two experts: eight warps each take an eighth of an expert's float32 weight row against
+// every token's float32 row; their partial sums are added in warp order.  The block that finishes last then
+// picks the experts and makes the lists.
+__global__ void __launch_bounds__(SMALL_WARPS * 32)
+router_small_kernel(const float* __restrict__ act, const float* __restrict__ router, int width, float* __restrict__ logits,
+                    unsigned int* __restrict__ ticket, SmallRouteParams p) {
+    extern __shared__ float sm[];
+    __shared__ int s_ids[SMALL_MAX_ASSIGN];
+    __shared__ float s_part[SMALL_WARPS][ROUTER_SMALL_TOKENS];
+    __shared__ int s_last;
+    constexpr int WARPS_PER_EXPERT = SMALL_WARPS / ROUTER_SMALL_EXPERTS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = blockIdx.x * ROUTER_SMALL_EXPERTS + warp / WARPS_PER_EXPERT;
+    const int part = warp % WARPS_PER_EXPERT;
+    float acc[ROUTER_SMALL_TOKENS];
+#pragma unroll
+    for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) acc[j] = 0.f;
+    if (e < p.num_experts) {
+        const int vecs = width / 4;
+        const int per_part = (vecs + WARPS_PER_EXPERT - 1) / WARPS_PER_EXPERT;
+        const int begin = part * per_part, end = min(vecs, begin + per_part);
+        const float4* w = reinterpret_cast<const float4*>(router + (size_t)e * width);
+        for (int k = begin + lane; k < end; k += 32) {
+            const float4 wv = __ldg(w + k);
+#pragma unroll
+            for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) {
+                if (j < p.num_tokens) {
+                    const float4 xv = __ldg(reinterpret_cast<const float4*>(act + (size_t)j * width) + k);
+                    acc[j] += xv.x * wv.x + xv.y * wv.y + xv.z * wv.z + xv.w * wv.w;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) {
+        const float total = warp_sum(acc[j]);
+        if (lane == 0) s_part[warp][j] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x < ROUTER_SMALL_EXPERTS * ROUTER_SMALL_TOKENS) {
+        const int local = threadIdx.x / ROUTER_SMALL_TOKENS, j = threadIdx.x % ROUTER_SMALL_TOKENS;
+        const int expert = blockIdx.x * ROUTER_SMALL_EXPERTS + local;
+        if (expert < p.num_experts && j < p.num_tokens) {
+            float total = 0.f;
+            for (int w = 0; w < WARPS_PER_EXPERT; ++w) total += s_part[local * WARPS_PER_EXPERT + w][j];
+            logits[(size_t)j * p.num_experts + expert] = total;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int before = atomicAdd(ticket, 1u);
+        s_last = before == gridDim.x - 1;
+        if (s_last) *ticket = 0;                          // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    route_and_plan(p, sm, s_ids);
+}
+
+static int small_route_params(SmallRouteParams& p, size_t& smem, const float* logits, const float* bias, int num_tokens,
+                              int num_experts, int top_k, int renormalize, float routed_scale, int tile_rows, int* ids,
+                              float* weights, int* offsets, int* sorted_token, int* row_of_assign, int* tile_expert,
+                              int* tile_row0, int* num_tiles) {
+    FRB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "router: top_k %d is outside 1..%d experts", top_k, num_experts);
+    FRB_CHECK_ARG(num_tokens * top_k <= SMALL_MAX_ASSIGN, "small router: %d assignments exceed %d", num_tokens * top_k,
+                  SMALL_MAX_ASSIGN);
+    smem = (size_t)SMALL_WARPS * 2 * num_experts * sizeof(float) + (size_t)(3 * num_experts + 2) * sizeof(int);
+    FRB_CHECK_ARG(smem <= 160 * 1024, "small router: %d experts need %zu bytes of shared memory", num_experts, smem);
+    p.logits = logits; p.bias = bias; p.num_tokens = num_tokens; p.num_experts = num_experts; p.top_k = top_k;
+    p.renormalize = renormalize; p.routed_scale = routed_scale; p.tile_rows = tile_rows; p.ids = ids; p.weights = weights;
+    p.offsets = offsets; p.sorted_token = sorted_token; p.row_of_assign = row_of_assign; p.tile_expert = tile_expert;
+    p.tile_row0 = tile_row0; p.num_tiles = num_tiles;
+    return 0;
+}
+
 FRB_API int frb_route_plan_small(const float* logits, const float* bias, int num_tokens, int num_experts, int top_k,
                                  int renormalize, float routed_scale, int tile_rows, int* ids, float* weights, int* offsets,
                                  int* sorted_token, int* row_of_assign, int* tile_expert, int* tile_row0, int* num_tiles,
                                  cudaStream_t stream) {
     if (num_tokens == 0) return 0;
-    FRB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "router: top_k %d is outside 1..%d experts", top_k, num_experts);
-    FRB_CHECK_ARG(num_tokens * top_k <= SMALL_MAX_ASSIGN, "small router: %d assignments exceed %d", num_tokens * top_k,
-                  SMALL_MAX_ASSIGN);
-    const size_t smem = (size_t)SMALL_WARPS * 2 * num_experts * sizeof(float) + (size_t)(3 * num_experts + 2) * sizeof(int);
-    FRB_CHECK_ARG(smem <= 160 * 1024, "small router: %d experts need %zu bytes of shared memory", num_experts, smem);
+    SmallRouteParams p;
+    size_t smem;
+    if (small_route_params(p, smem, logits, bias, num_tokens, num_experts, top_k, renormalize, routed_scale, tile_rows, ids,
+                           weights, offsets, sorted_token, row_of_assign, tile_expert, tile_row0, num_tiles))
+        return -1;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(route_plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    route_plan_small_kernel<<<1, SMALL_WARPS * 32, smem, stream>>>(logits, bias, num_tokens, num_experts, top_k, renormalize,
-                                                                   routed_scale, tile_rows, ids, weights, offsets, sorted_token,
-                                                                   row_of_assign, tile_expert, tile_row0, num_tiles);
+    route_plan_small_kernel<<<1, SMALL_WARPS * 32, smem, stream>>>(p);
     FRB_RETURN_LAUNCH("route_plan_small");
+}
+
+// act [T, width] float32 rows, router [E, width] float32 -> logits [T, E] (scratch, kept) and all of the above.
+// ticket: one unsigned int on the device, zero before the first call (the kernel leaves it zero).
+FRB_API int frb_router_small(const float* act, const float* router, int width, float* logits, unsigned int* ticket,
+                             const float* bias, int num_tokens, int num_experts, int top_k, int renormalize,
+                             float routed_scale, int tile_rows, int* ids, float* weights, int* offsets, int* sorted_token,
+                             int* row_of_assign, int* tile_expert, int* tile_row0, int* num_tiles, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    FRB_CHECK_ARG(width % 4 == 0 && ((uintptr_t)act & 15) == 0 && ((uintptr_t)router & 15) == 0,
+                  "small router: a width of %d (or an unaligned operand) does not allow 16-byte loads", width);
+    FRB_CHECK_ARG(num_tokens <= ROUTER_SMALL_TOKENS, "small router: %d tokens exceed %d", num_tokens, ROUTER_SMALL_TOKENS);
+    SmallRouteParams p;
+    size_t smem;
+    if (small_route_params(p, smem, logits, bias, num_tokens, num_experts, top_k, renormalize, routed_scale, tile_rows, ids,
+                           weights, offsets, sorted_token, row_of_assign, tile_expert, tile_row0, num_tiles))
+        return -1;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int blocks = (num_experts + ROUTER_SMALL_EXPERTS - 1) / ROUTER_SMALL_EXPERTS;
+    router_small_kernel<<<blocks, SMALL_WARPS * 32, smem, stream>>>(act, router, width, logits, ticket, p);
+    FRB_RETURN_LAUNCH("router_small");
 }
 
 // ----------------------------------------------------------------------------- weighted sum of expert outputs

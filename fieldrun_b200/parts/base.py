@@ -57,8 +57,23 @@ class Part:
             raise KeyError(f"part {self.spec.kind!r} was given no checkpoint name for its tensor {local!r}") from None
 
 
+class DeferredUpdate:
+    """An update of the residual stream that its maker has not summed up yet, so that the norm which adds it
+    can do the sum while it reads the stream.  ``materialize`` gives the plain float32 tensor [T, width]."""
+
+    def materialize(self, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+def as_tensor(ctx, update):
+    """The update as a float32 tensor, whatever form it came in (None stays None)."""
+    return update.materialize(ctx) if isinstance(update, DeferredUpdate) else update
+
+
 class Norm(Part):
-    def forward(self, ctx, x: torch.Tensor, *, delta: Optional[torch.Tensor] = None,
+    accepts_deferred: bool = False       # whether ``delta`` may be a DeferredUpdate of a kind this norm knows
+
+    def forward(self, ctx, x: torch.Tensor, *, delta=None,
                 rows: Optional[torch.Tensor] = None, want32: bool = False, write_back: bool = True):
         raise NotImplementedError
 
@@ -89,6 +104,10 @@ class FeedForward(Part):
 
     def forward(self, ctx, act: torch.Tensor, act32: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_deferred(self, ctx, act: torch.Tensor, act32: Optional[torch.Tensor]):
+        """Like ``forward``, but may return a :class:`DeferredUpdate`."""
+        return self.forward(ctx, act, act32)
 
 
 class Block:

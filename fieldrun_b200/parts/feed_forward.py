@@ -17,11 +17,24 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
-from .base import FeedForward, register_part
+from .base import DeferredUpdate, FeedForward, register_part
 from .linear import linear
 
 TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
 TENSOR_CORE_ROWS_PER_EXPERT = 12     # above this many rows per expert (on average) a step runs on tcgen05
+
+
+class ExpertUpdate(DeferredUpdate):
+    """The outputs of each token's experts, not yet summed: update[t] = sum over ranks r, in rank order, of
+    weights[t, r] * y[row_of_assign[t * k + r]]."""
+
+    def __init__(self, y: torch.Tensor, weights: torch.Tensor, row_of_assign: torch.Tensor):
+        self.y, self.weights, self.row_of_assign = y, weights, row_of_assign
+
+    def materialize(self, ctx) -> torch.Tensor:
+        out = ctx.buffer("experts.out", (self.weights.shape[0], self.y.shape[1]), torch.float32)
+        ops.expert_combine(self.y, self.weights, self.row_of_assign, out)
+        return out
 
 
 class RoutedExperts(FeedForward):
@@ -158,7 +171,6 @@ class RoutedExperts(FeedForward):
         """For steps of few tokens: choice and lists in one launch."""
         tokens = act32.shape[0]
         n = tokens * self.top_k
-        logits = linear(act32, self.router)
         tile_rows = self.tile_rows(n)
         max_tiles = (n + tile_rows - 1) // tile_rows + min(self.num_experts, n)
         ids = ctx.buffer("experts.ids", (tokens, self.top_k), torch.int32)
@@ -172,12 +184,22 @@ class RoutedExperts(FeedForward):
             "num_tiles": ctx.buffer("experts.num_tiles", (1,), torch.int32),
             "max_tiles": max_tiles, "rows": n, "tile_rows": tile_rows,
         }
-        ops.route_plan_small(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, tile_rows, ids, weights,
-                             p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"], p["tile_row0"],
-                             p["num_tiles"])
+        if self.hidden_size % 4 == 0 and tokens <= ops.ROUTER_SMALL_TOKENS:
+            logits = ctx.buffer("experts.logits", (tokens, self.num_experts), torch.float32)
+            ops.router_small(act32, self.router, logits, self.bias, self.top_k, self.renormalize, self.routed_scale, tile_rows,
+                             ids, weights, p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"],
+                             p["tile_row0"], p["num_tiles"])
+        else:
+            logits = linear(act32, self.router)
+            ops.route_plan_small(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, tile_rows, ids, weights,
+                                 p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"], p["tile_row0"],
+                                 p["num_tiles"])
         return ids, weights, p
 
     def forward(self, ctx, act, act32):
+        return self.forward_deferred(ctx, act, act32).materialize(ctx)
+
+    def forward_deferred(self, ctx, act, act32):
         if act32 is None:
             raise ValueError("routed experts need the normed rows in float32 for the router")
         if act.shape[0] * self.top_k <= ops.SMALL_ROUTE_ASSIGNMENTS and self.num_experts <= 1024:
@@ -190,9 +212,7 @@ class RoutedExperts(FeedForward):
                 self.on_route(ids)
             p = self.plan(ctx, ids)
         y = self.experts(ctx, act, p)
-        out = ctx.buffer("experts.out", (act.shape[0], self.hidden_size), torch.float32)
-        ops.expert_combine(y, weights, p["row_of_assign"], out)
-        return out
+        return ExpertUpdate(y, weights, p["row_of_assign"])
 
 
 class DenseGatedUnit(FeedForward):

@@ -9,7 +9,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import VECTOR, TensorNeed, TensorSource
-from .base import Norm, register_part
+from .base import Norm, as_tensor, register_part
 
 
 class RMSNorm(Norm):
@@ -27,15 +27,23 @@ class RMSNorm(Norm):
     def load(self, source: TensorSource) -> None:
         self.weight = source.fetch(self.tensor_needs()[0])
 
+    accepts_deferred = True
+
     def forward(self, ctx, x, *, delta=None, rows=None, want32=False, write_back=True):
+        from .feed_forward import ExpertUpdate
+        experts = None
+        if isinstance(delta, ExpertUpdate):
+            experts, delta = (delta.y, delta.weights, delta.row_of_assign), None
+        else:
+            delta = as_tensor(ctx, delta)
         count = rows.numel() if rows is not None else x.shape[0]
         out = ctx.buffer(f"norm.out.{self.width}", (count, self.width), self.dtype)
         out32 = None
         if want32:
             out32 = out if self.dtype == torch.float32 else ctx.buffer(f"norm.out32.{self.width}", (count, self.width),
                                                                        torch.float32)
-        ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows,
-                    out32=None if out32 is out else out32, write_back=write_back and delta is not None)
+        ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows, out32=None if out32 is out else out32,
+                    write_back=write_back and (delta is not None or experts is not None), experts=experts)
         return out, out32
 
 

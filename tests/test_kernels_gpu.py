@@ -591,3 +591,59 @@ def test_gather_rows():
     out = torch.empty(37, 64, dtype=torch.bfloat16, device=DEV)
     ops().gather_rows(x, dev(rows), out)
     assert torch.equal(out, x[torch.as_tensor(rows, device=DEV).long()])
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,width", [(1, 8, 256, 3072), (8, 8, 256, 3072), (3, 8, 255, 500), (7, 3, 11, 96), (5, 1, 1, 64)])
+def test_router_logits_choice_and_lists_in_one_launch(tokens, top_k, experts, width):
+    rng = np.random.default_rng(19)
+    act = dev(rng.normal(size=(tokens, width)).astype(np.float32))
+    router = dev((rng.normal(size=(experts, width)) * 0.05).astype(np.float32))
+    bias = dev((0.1 * rng.normal(size=experts)).astype(np.float32))
+    n = tokens * top_k
+    tile_rows = 8
+    max_tiles = (n + tile_rows - 1) // tile_rows + min(experts, n)
+    i32 = lambda k: torch.full((k,), -7, dtype=torch.int32, device=DEV)
+
+    def buffers():
+        return dict(ids=torch.empty(tokens, top_k, dtype=torch.int32, device=DEV),
+                    weights=torch.empty(tokens, top_k, dtype=torch.float32, device=DEV), offsets=i32(experts + 1),
+                    sorted_token=i32(n), row_of_assign=i32(n), tile_expert=i32(max_tiles), tile_row0=i32(max_tiles),
+                    num_tiles=i32(1))
+
+    logits = torch.empty(tokens, experts, dtype=torch.float32, device=DEV)
+    for attempt in range(2):                                         # twice: the ticket must be left ready
+        a = buffers()
+        ops().router_small(act, router, logits, bias, top_k, True, 1.0, tile_rows, a["ids"], a["weights"], a["offsets"],
+                           a["sorted_token"], a["row_of_assign"], a["tile_expert"], a["tile_row0"], a["num_tiles"])
+        ref_logits = f64(act) @ f64(router).T
+        close(f64(logits), ref_logits, 2e-6, "router logits")
+        b = buffers()
+        ops().route_plan_small(logits, bias, top_k, True, 1.0, tile_rows, b["ids"], b["weights"], b["offsets"], b["sorted_token"],
+                               b["row_of_assign"], b["tile_expert"], b["tile_row0"], b["num_tiles"])
+        nt = int(a["num_tiles"].item())
+        assert nt == int(b["num_tiles"].item())
+        for name in ("ids", "weights", "offsets", "sorted_token", "row_of_assign"):
+            assert torch.equal(a[name], b[name]), name
+        for name in ("tile_expert", "tile_row0"):
+            assert torch.equal(a[name][:nt], b[name][:nt]), name
+
+
+def test_norm_adds_the_experts_outputs_in_rank_order():
+    rng = np.random.default_rng(20)
+    tokens, top_k, width = 9, 3, 200
+    x = rng.normal(size=(tokens, width)).astype(np.float32)
+    y = rng.normal(size=(tokens * top_k, width)).astype(np.float32)
+    ew = rng.random(size=(tokens, top_k)).astype(np.float32)
+    rowmap = rng.permutation(tokens * top_k).astype(np.int32)
+    w = (1 + 0.1 * rng.normal(size=width)).astype(np.float32)
+    total = x.astype(np.float64).copy()
+    for t in range(tokens):
+        s = np.zeros(width, dtype=np.float32)
+        for r in range(top_k):
+            s = s + ew[t, r] * y[rowmap[t * top_k + r]]
+        total[t] += s
+    xd = dev(x)
+    out = torch.empty(tokens, width, dtype=torch.float32, device=DEV)
+    ops().rmsnorm(xd, dev(w), 1e-5, out, write_back=True, experts=(dev(y), dev(ew), dev(rowmap)))
+    close(f64(xd), total, 1e-6, "stream with the experts' sum")
+    close(f64(out), pm.rms_norm(total, w.astype(np.float64), 1e-5), 3e-6, "norm of it")
