@@ -50,8 +50,8 @@ __device__ __forceinline__ void stage_page(uint4* k_tile, uint4* vt_tile, const 
 // grid (tile of 16 queries, kv head).  The warps of a block take the query heads of the kv head's group:
 // they need the same keys and values, which the block copies page by page into two stages of shared memory
 // with cp.async, the next page on its way while the current one is multiplied.
-template <int HD>
-__global__ void __launch_bounds__(256) attention_prefill_mma_kernel(PrefillAttnParams p) {
+template <int HD, int MAX_WARPS>
+__global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attention_prefill_mma_kernel(PrefillAttnParams p) {
     extern __shared__ uint4 stages[];                   // 2 x (K tile, V^T tile), FRB_PAGE * HD / 8 chunks each
     constexpr int TILE = FRB_PAGE * HD / 8;
     const int tile = blockIdx.x, kvh = blockIdx.y;
@@ -134,10 +134,17 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
     const int nwarps = group < 8 ? group : 8;
     dim3 grid(num_tiles, num_kv_heads);
     const size_t smem = (size_t)4 * FRB_PAGE * head_dim * sizeof(bf16);           // two stages of K and V^T
+    // groups of up to 6 heads: blocks of at most 192 threads, held to two per SM; larger groups: 256 threads
 #define LAUNCH(HD)                                                                                                  \
-    if (smem > 48 * 1024)                                                                                           \
-        cudaFuncSetAttribute(attention_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    attention_prefill_mma_kernel<HD><<<grid, 32 * nwarps, smem, stream>>>(p)
+    if (nwarps <= 6) {                                                                                              \
+        if (smem > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(attention_prefill_mma_kernel<HD, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        attention_prefill_mma_kernel<HD, 6><<<grid, 32 * nwarps, smem, stream>>>(p);                                \
+    } else {                                                                                                        \
+        if (smem > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(attention_prefill_mma_kernel<HD, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        attention_prefill_mma_kernel<HD, 8><<<grid, 32 * nwarps, smem, stream>>>(p);                                \
+    }
     if (head_dim == 32) { LAUNCH(32); } else if (head_dim == 64) { LAUNCH(64); } else if (head_dim == 96) { LAUNCH(96); } else { LAUNCH(128); }
 #undef LAUNCH
     FRB_RETURN_LAUNCH("attention_prefill_mma");

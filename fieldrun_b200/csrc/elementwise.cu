@@ -48,7 +48,9 @@ FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype
 
 // ----------------------------------------------------------------------------- RMSNorm (+ residual add)
 
-#define NORM_BLOCK 1024
+// Rows are one block each.  A step of few rows takes blocks of 1024 threads (the row's latency is the step's);
+// a step of many rows takes blocks of 256 (more blocks per SM, less waiting at the block's barriers).
+#define NORM_FEW_ROWS 64
 #define NORM_MAX_TOP_K 32
 
 // The update of the residual stream may come as the outputs of a token's experts, not yet summed:
@@ -64,7 +66,7 @@ struct ExpertSum {
 // One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]) (+ the experts' sum of
 // src); if write_back the sum is stored to x[src] (the residual stream).
 // out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and, when out32 is given, in float32 as well.
-template <typename OutT, typename WT>
+template <typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum experts, const int* __restrict__ rows,
                const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
@@ -118,10 +120,17 @@ FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, con
     const size_t smem = (size_t)width * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "rmsnorm: width %d needs %zu bytes of shared memory, more than 200 KB", width, smem);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
-        auto kernel = rmsnorm_kernel<OutT, WT>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<num_rows, NORM_BLOCK, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out,
-                                                       out32, write_back);
+        if (num_rows <= NORM_FEW_ROWS) {
+            auto kernel = rmsnorm_kernel<OutT, WT, 1024>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<num_rows, 1024, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
+                                                     write_back);
+        } else {
+            auto kernel = rmsnorm_kernel<OutT, WT, 256>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<num_rows, 256, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
+                                                    write_back);
+        }
     }));
     FRB_RETURN_LAUNCH("rmsnorm");
 }
@@ -151,7 +160,7 @@ __device__ __forceinline__ float normed(const float* raw, const WT* w, float rin
 
 // One block per token.  The raw Q and K rows sit in shared memory; each thread produces output elements
 // from the raw values of its own element and of its rotation partner.
-template <typename InT, typename OutT, typename WT>
+template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     extern __shared__ float raw[];           // [(nh + nkv) * hd] : Q row then K row
     __shared__ float scratch[32];
@@ -236,9 +245,15 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + kv heads) * head_dim = %d needs more than 200 KB of shared memory",
                   (num_heads + num_kv_heads) * head_dim);
     FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
-        auto kernel = qkv_prepare_kernel<InT, OutT, WT>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<num_tokens, NORM_BLOCK, smem, stream>>>(p);
+        if (num_tokens <= NORM_FEW_ROWS) {
+            auto kernel = qkv_prepare_kernel<InT, OutT, WT, 1024>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<num_tokens, 1024, smem, stream>>>(p);
+        } else {
+            auto kernel = qkv_prepare_kernel<InT, OutT, WT, 256>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<num_tokens, 256, smem, stream>>>(p);
+        }
     })));
     FRB_RETURN_LAUNCH("qkv_prepare");
 }

@@ -101,7 +101,10 @@ plan_count_kernel(const int* __restrict__ ids, int num_assign, int num_experts, 
 __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_scan_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int tile_rows, int* __restrict__ offsets,
                  int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
-    extern __shared__ int total[];       // [E]
+    extern __shared__ int total[];       // [E] totals, then [E + 1] first rows, then [E + 1] first tiles
+    int* first = total + num_experts;
+    int* first_tile = first + num_experts + 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
         int run = 0;
         for (int c = 0; c < num_chunks; ++c) {
@@ -112,46 +115,71 @@ plan_scan_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int 
         total[e] = run;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, tiles = 0;
-        for (int e = 0; e < num_experts; ++e) {
-            offsets[e] = run;
-            for (int r = 0; r < total[e]; r += tile_rows) {
-                tile_expert[tiles] = e;
-                tile_row0[tiles] = run + r;
-                ++tiles;
-            }
-            run += total[e];
+    if (warp == 0) {                     // exclusive sums over the experts: each lane a run of experts, then a warp scan
+        const int per_lane = (num_experts + 31) / 32;
+        const int begin = lane * per_lane, end = min(num_experts, begin + per_lane);
+        int rows = 0, tiles = 0;
+        for (int e = begin; e < end; ++e) { rows += total[e]; tiles += (total[e] + tile_rows - 1) / tile_rows; }
+        int rows_before = rows, tiles_before = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, rows_before, o), c = __shfl_up_sync(0xffffffffu, tiles_before, o);
+            if (lane >= o) { rows_before += r; tiles_before += c; }
         }
-        offsets[num_experts] = run;
-        num_tiles[0] = tiles;
+        const int all_rows = __shfl_sync(0xffffffffu, rows_before, 31), all_tiles = __shfl_sync(0xffffffffu, tiles_before, 31);
+        rows_before -= rows;
+        tiles_before -= tiles;
+        for (int e = begin; e < end; ++e) {
+            first[e] = rows_before;
+            first_tile[e] = tiles_before;
+            rows_before += total[e];
+            tiles_before += (total[e] + tile_rows - 1) / tile_rows;
+        }
+        if (lane == 0) { first[num_experts] = all_rows; num_tiles[0] = all_tiles; }
     }
     __syncthreads();
+    for (int e = threadIdx.x; e <= num_experts; e += PLAN_BLOCK) offsets[e] = first[e];
     for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
-        const int first = offsets[e];
-        for (int c = 0; c < num_chunks; ++c) counts[(size_t)c * num_experts + e] += first;
+        int tile = first_tile[e];
+        for (int r = 0; r < total[e]; r += tile_rows, ++tile) {
+            tile_expert[tile] = e;
+            tile_row0[tile] = first[e] + r;
+        }
+        for (int c = 0; c < num_chunks; ++c) counts[(size_t)c * num_experts + e] += first[e];
     }
 }
 
-// Places every assignment a = t*k + r, in order, behind the earlier ones of the same expert.
+// Places every assignment a = t*k + r, in order, behind the earlier ones of the same expert.  One warp walks
+// the chunk 32 assignments at a time: lanes with the same expert find one another with a match, take
+// consecutive places from the expert's running counter, and the lowest of them moves the counter on.
 __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_fill_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int top_k, const int* __restrict__ counts,
                  int* __restrict__ sorted_token, int* __restrict__ row_of_assign) {
-    __shared__ int chunk_ids[PLAN_CHUNK];
+    extern __shared__ int next_place[];          // [E]
+    __shared__ int place[PLAN_CHUNK];
     const int c = blockIdx.x;
     const int begin = c * PLAN_CHUNK, n = min(num_assign - begin, PLAN_CHUNK);
-    for (int i = threadIdx.x; i < n; i += PLAN_BLOCK) chunk_ids[i] = ids[begin + i];
+    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) next_place[e] = counts[(size_t)c * num_experts + e];
     __syncthreads();
-    for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) {
-        int at = counts[(size_t)c * num_experts + e];
-        for (int i = 0; i < n; ++i) {
-            if (chunk_ids[i] == e) {
-                const int a = begin + i;
-                sorted_token[at] = a / top_k;
-                row_of_assign[a] = at;
-                ++at;
-            }
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        for (int base = 0; base < n; base += 32) {
+            const int i = base + lane;
+            const bool live = i < n;
+            const int e = live ? ids[begin + i] : -1 - lane;             // idle lanes match nobody
+            const unsigned same = __match_any_sync(0xffffffffu, e);
+            const int rank = __popc(same & ((1u << lane) - 1));
+            if (live) place[i] = next_place[e] + rank;
+            __syncwarp();
+            if (live && rank == 0) next_place[e] += __popc(same);
+            __syncwarp();
         }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += PLAN_BLOCK) {
+        const int a = begin + i;
+        sorted_token[place[i]] = a / top_k;
+        row_of_assign[a] = place[i];
     }
 }
 
@@ -162,14 +190,14 @@ FRB_API int frb_expert_plan(const int* ids, int num_tokens, int top_k, int num_e
                             int* num_tiles, cudaStream_t stream) {
     const int num_assign = num_tokens * top_k;
     if (num_assign == 0) return 0;
-    FRB_CHECK_ARG(num_experts * sizeof(int) <= 48 * 1024, "expert plan: %d experts exceed the kernel's 12288", num_experts);
+    FRB_CHECK_ARG((3 * num_experts + 2) * sizeof(int) <= 48 * 1024, "expert plan: %d experts exceed the kernel's 4095", num_experts);
     const int chunks = (num_assign + PLAN_CHUNK - 1) / PLAN_CHUNK;
     const size_t smem = (size_t)num_experts * sizeof(int);
     plan_count_kernel<<<chunks, PLAN_BLOCK, smem, stream>>>(ids, num_assign, num_experts, counts);
-    plan_scan_kernel<<<1, PLAN_BLOCK, smem, stream>>>(counts, chunks, num_experts, tile_rows, offsets, tile_expert,
-                                                      tile_row0, num_tiles);
-    plan_fill_kernel<<<chunks, PLAN_BLOCK, 0, stream>>>(ids, num_assign, num_experts, top_k, counts, sorted_token,
-                                                        row_of_assign);
+    plan_scan_kernel<<<1, PLAN_BLOCK, 3 * smem + 2 * sizeof(int), stream>>>(counts, chunks, num_experts, tile_rows, offsets,
+                                                                          tile_expert, tile_row0, num_tiles);
+    plan_fill_kernel<<<chunks, PLAN_BLOCK, smem, stream>>>(ids, num_assign, num_experts, top_k, counts, sorted_token,
+                                                           row_of_assign);
     FRB_RETURN_LAUNCH("expert_plan");
 }
 
