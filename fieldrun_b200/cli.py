@@ -54,6 +54,16 @@ def _random(argv: list[str]) -> int:
 
 
 def main(argv: list[str] | None = None) -> int:
+    """Runs the command; an error the user can act on becomes one line and exit status 1, as the reference
+    turns its panics into one-line messages (src/main.rs:115-126)."""
+    try:
+        return _main(argv)
+    except (OSError, ValueError, RuntimeError, KeyError) as err:
+        print(f"[fieldrun_b200] error: {err}", file=sys.stderr)
+        return 1
+
+
+def _main(argv: list[str] | None = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "random":
         return _random(argv[1:])
