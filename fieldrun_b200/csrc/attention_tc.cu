@@ -1,0 +1,399 @@
+// Many-token attention on the fifth-generation tensor cores (tcgen05), for prompts in bfloat16.
+//
+// The formula is the reference's (src/minimax.rs:270-281): s = q.k * scale over the keys a query may see,
+// p = softmax(s), out = p V.  A block takes 128 queries of one head.  For every cache page of 64 keys:
+//   S = Q K^T      tcgen05.mma 128 x 64 x HD, Q and the page's keys in shared memory (TMA, 128-byte swizzle),
+//                  S in tensor memory, two buffers so that the next page's product runs during this page's softmax;
+//   softmax        four warps, one thread per query row: S comes back with tcgen05.ld, running maximum and sum
+//                  in float32 registers; P (bfloat16) goes back into tensor memory with tcgen05.st;
+//   O += P V       tcgen05.mma 128 x HD x 64 with P as the tensor-memory operand and the page's transposed
+//                  values [HD][64 keys] as the shared-memory operand; O stays in tensor memory.
+// The running maximum of a row is only raised when the page's maximum exceeds it by more than 8 (in units of
+// log2): the weights are then at most 2^8, the result is the same after the division by the row's sum, and
+// O has to be rescaled (read, multiplied, written back) only on those rare pages.
+//
+// Every wait on an mbarrier gives up after about a second (at once when another wait of the block has given
+// up), sets `status`, and the block leaves through the common exit, which frees the tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define AT_QUERIES 128
+#define AT_THREADS 192         // warp 0: TMA producer, warp 1: MMA issuer and tensor-memory owner, warps 2-5: softmax
+#define AT_STAGES 3
+#define AT_WAIT_CYCLES (2000000000ll)
+#define AT_RAISE 8.0f          // the running maximum follows a page's maximum only beyond this margin
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void bar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// false when the phase did not complete in time, or another wait of this block already gave up
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+    const uint32_t addr = smem_addr(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (*failed || clock64() - start > AT_WAIT_CYCLES) { *failed = 1; return false; }
+    }
+}
+
+__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// A from tensor memory
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+}  // namespace
+
+struct AttnTcParams {
+    const int* page_table;
+    const int* tile_seq;       // [tiles]
+    const int* tile_q0;        // [tiles] first row of the tile among its sequence's new tokens
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_q_len;
+    const int* cu_q_len;
+    bf16* out;                 // [T, nh * HD]
+    int* status;
+    float scale2;              // softmax scale * log2(e)
+    int window, max_pages, num_heads, num_kv_heads;
+};
+
+// grid (tile of 128 queries, head)
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t q_full, kv_full[AT_STAGES], kv_empty[AT_STAGES], s_full[2], s_free[2], p_full[2], pv_done[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed_flag;
+    volatile int* failed = &failed_flag;
+    constexpr int KBLOCKS = HD / 64;                           // 64 dims = one 128-byte swizzled row
+    constexpr uint32_t Q_BYTES = AT_QUERIES * HD * 2, K_BYTES = FRB_PAGE * HD * 2, V_BYTES = HD * FRB_PAGE * 2;
+    constexpr uint32_t S_COL0 = 0, O_COL = 128, P_COL0 = O_COL + HD;       // S: 2 x 64 columns, O: HD, P: 2 x 32
+    constexpr uint32_t TMEM_COLS = (P_COL0 + 64) <= 256 ? 256 : 512;
+
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = p.num_heads / p.num_kv_heads, kvh = head / group;
+    const int b = p.tile_seq[tile], q0 = p.tile_q0[tile];
+    const int q_len = p.seq_q_len[b], start = p.seq_start[b], tok0 = p.cu_q_len[b] + q0;
+    const int* table = p.page_table + (size_t)p.seq_slot[b] * p.max_pages;
+    const int last_key = start + min(q0 + AT_QUERIES - 1, q_len - 1);
+    const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int first_page = first_key / FRB_PAGE, num_pages = last_key / FRB_PAGE - first_page + 1;
+
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_tile = base;                                    // KBLOCKS tiles [128 x 64]
+    uint8_t* stage0 = base + Q_BYTES;                          // per stage: K (KBLOCKS tiles [64 x 64]) then V^T ([HD x 64])
+
+    if (threadIdx.x == 0) {
+        bar_init(&q_full, 1);
+        for (int s = 0; s < AT_STAGES; ++s) { bar_init(&kv_full[s], 1); bar_init(&kv_empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { bar_init(&s_full[i], 1); bar_init(&s_free[i], 4); bar_init(&p_full[i], 4); bar_init(&pv_done[i], 1); }
+        failed_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bar_expect(&q_full, Q_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < KBLOCKS; ++kb)
+                tma_2d(q_tile + kb * (AT_QUERIES * 128), &map_q, head * HD + kb * 64, tok0, &q_full);
+            for (int i = 0; i < num_pages; ++i) {
+                const int s = i % AT_STAGES;
+                if (!bar_wait(&kv_empty[s], ((i / AT_STAGES) & 1) ^ 1, failed)) { atomicExch(p.status, 11); break; }
+                const int page = table[first_page + i];
+                uint8_t* dst = stage0 + (size_t)s * (K_BYTES + V_BYTES);
+                bar_expect(&kv_full[s], K_BYTES + V_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < KBLOCKS; ++kb)
+                    tma_2d(dst + kb * (FRB_PAGE * 128), &map_k, kb * 64, (page * p.num_kv_heads + kvh) * FRB_PAGE, &kv_full[s]);
+                tma_2d(dst + K_BYTES, &map_v, 0, (page * p.num_kv_heads + kvh) * HD, &kv_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // float32 accumulate, bf16 operands, K-major; S: M 128 x N 64; O: M 128 x N HD
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FRB_PAGE >> 3) << 17) | ((uint32_t)(AT_QUERIES >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(AT_QUERIES >> 4) << 24);
+            const uint32_t q_addr = smem_addr(q_tile);
+            bool ok = bar_wait(&q_full, 0, failed);
+            if (!ok) atomicExch(p.status, 12);
+            // issues S_i = Q K_i^T into S buffer i & 1
+            auto issue_scores = [&](int i) -> bool {
+                const int s = i % AT_STAGES;
+                if (!bar_wait(&kv_full[s], (i / AT_STAGES) & 1, failed)) { atomicExch(p.status, 13); return false; }
+                if (i >= 2 && !bar_wait(&s_free[i & 1], ((i - 2) >> 1) & 1, failed)) { atomicExch(p.status, 14); return false; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_addr(stage0 + (size_t)s * (K_BYTES + V_BYTES));
+#pragma unroll
+                for (int kb = 0; kb < KBLOCKS; ++kb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_ss(tmem + S_COL0 + 64 * (i & 1), tile_desc(q_addr + kb * (AT_QUERIES * 128) + k * 32),
+                               tile_desc(k_addr + kb * (FRB_PAGE * 128) + k * 32), idesc_s, (kb | k) != 0);
+                mma_commit(&s_full[i & 1]);
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int i = 0; i < num_pages && ok; ++i) {
+                if (i + 1 < num_pages) ok = issue_scores(i + 1);
+                if (!ok) break;
+                if (!bar_wait(&p_full[i & 1], (i >> 1) & 1, failed)) { atomicExch(p.status, 15); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = i % AT_STAGES;
+                const uint32_t v_addr = smem_addr(stage0 + (size_t)s * (K_BYTES + V_BYTES) + K_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)                    // 16 keys per MMA: 8 columns of packed P, 32 bytes of a V^T row
+                    mma_ts(tmem + O_COL, tmem + P_COL0 + 32 * (i & 1) + 8 * k, tile_desc(v_addr + k * 32), idesc_o, (i | k) != 0);
+                mma_commit(&kv_empty[s]);
+                mma_commit(&pv_done[i & 1]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                   // the query row of this thread = its lane of tensor memory
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool valid = q0 + row < q_len;
+        const int hi = valid ? start + q0 + row : -1;
+        const int lo = (valid && p.window > 0) ? max(0, hi - p.window + 1) : 0;
+        float m_used = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int i = 0; i < num_pages && ok; ++i) {
+            if (!bar_wait(&s_full[i & 1], (i >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 16); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t raw[4][16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld16(lane_base + S_COL0 + 64 * (i & 1) + 16 * c, raw[c]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(&s_free[i & 1]);
+            const int key0 = (first_page + i) * FRB_PAGE;
+            float page_max = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int key = key0 + 16 * c + j;
+                    const float v = (key >= lo && key <= hi) ? __uint_as_float(raw[c][j]) * p.scale2 : -INFINITY;
+                    raw[c][j] = __float_as_uint(v);
+                    page_max = fmaxf(page_max, v);
+                }
+            float corr = 1.f;
+            const bool raise = page_max > m_used + AT_RAISE;   // also true on the first page with a visible key
+            if (raise) { corr = exp2f(m_used - page_max); m_used = page_max; }
+            const float m_sub = m_used == -INFINITY ? 0.f : m_used;
+            float sum = 0.f;
+            uint32_t packed[2][16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float a = exp2f(__uint_as_float(raw[c][j]) - m_sub), bb = exp2f(__uint_as_float(raw[c][j + 1]) - m_sub);
+                    sum += a + bb;
+                    packed[c >> 1][(c & 1) * 8 + (j >> 1)] = pack2(a, bb);
+                }
+            l_sum = l_sum * corr + sum;
+            if (i >= 2 && !bar_wait(&pv_done[i & 1], ((i - 2) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 17); ok = false; break; }
+            if (i > 0 && __any_sync(0xffffffffu, raise)) {     // rare: O must follow the new maximum
+                if (!bar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 18); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < HD / 16; ++c) {
+                    uint32_t o[16];
+                    tmem_ld16(lane_base + O_COL + 16 * c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                    tmem_st16(lane_base + O_COL + 16 * c, o);
+                }
+            }
+            tmem_st16(lane_base + P_COL0 + 32 * (i & 1), packed[0]);
+            tmem_st16(lane_base + P_COL0 + 32 * (i & 1) + 16, packed[1]);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(&p_full[i & 1]);
+        }
+        if (ok) {
+            const int last = num_pages - 1;
+            if (!bar_wait(&pv_done[last & 1], (last >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            bf16* dst = p.out + ((size_t)(tok0 + row) * p.num_heads + head) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 16; ++c) {
+                uint32_t o[16];
+                tmem_ld16(lane_base + O_COL + 16 * c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (valid) {
+                    uint4 lo4, hi4;
+                    lo4.x = pack2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+                    lo4.y = pack2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+                    lo4.z = pack2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+                    lo4.w = pack2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+                    hi4.x = pack2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+                    hi4.y = pack2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                    hi4.z = pack2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                    hi4.w = pack2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                    reinterpret_cast<uint4*>(dst + 16 * c)[0] = lo4;
+                    reinterpret_cast<uint4*>(dst + 16 * c)[1] = hi4;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (failed_flag && warp == 0 && lane == 0) {
+        // copies may still be on their way into this block's shared memory: give them a bounded time to land
+        int zero = 0;
+        bar_wait(&q_full, 0, &zero);
+        for (int s = 0; s < AT_STAGES; ++s) { zero = 0; bar_wait(&kv_full[s], 0, &zero); }
+    }
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+// ----------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encoder() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)ptr;
+    }
+    return fn;
+}
+
+// row-major bf16 [rows, cols]; boxes of [box_rows, 64 columns], 128-byte swizzle, zeros outside
+static bool map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeFn fn = encoder();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q bf16 [num_tokens, nh, hd]; k_pages [pages, nkv, 64, hd]; v_pages [pages, nkv, hd, 64]; tiles of 128 queries.
+// status: one int on the device, zero before the call.
+FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* k_pages, const void* v_pages, int num_pages,
+                                     const int* page_table, int max_pages, const int* tile_seq, const int* tile_q0,
+                                     int num_tiles, const int* seq_slot, const int* seq_start, const int* seq_q_len,
+                                     const int* cu_q_len, void* out, int num_heads, int num_kv_heads, int head_dim, float scale,
+                                     int window, int* status, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    FRB_CHECK_ARG(head_dim == 64 || head_dim == 128, "tensor-core attention: head_dim %d is neither 64 nor 128", head_dim);
+    FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && num_heads <= 65535, "tensor-core attention: %d heads over %d kv heads",
+                  num_heads, num_kv_heads);
+    CUtensorMap map_q, map_k, map_v;
+    const uint64_t kv_rows = (uint64_t)num_pages * num_kv_heads;
+    FRB_CHECK_ARG(map_2d(&map_q, q, num_tokens, (uint64_t)num_heads * head_dim, AT_QUERIES) &&
+                  map_2d(&map_k, k_pages, kv_rows * FRB_PAGE, head_dim, FRB_PAGE) &&
+                  map_2d(&map_v, v_pages, kv_rows * head_dim, FRB_PAGE, head_dim),
+                  "tensor-core attention: cuTensorMapEncodeTiled failed or is not available");
+    AttnTcParams p;
+    p.page_table = page_table; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start;
+    p.seq_q_len = seq_q_len; p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.status = status;
+    p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads;
+    const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
+    dim3 grid(num_tiles, num_heads);
+    if (head_dim == 128) {
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_prefill_tc_kernel<128><<<grid, AT_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+    } else {
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_prefill_tc_kernel<64><<<grid, AT_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+    }
+    FRB_RETURN_LAUNCH("attention_prefill_tc");
+}

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "frb_router_small": "ppipppiiiifipppppppp",
     "frb_expert_gemm_tc": "pipippppiipiiip",
     "frb_gather_rows_bf16": "pppii",
+    "frb_attention_prefill_tc": "pippipippipppppiiifip",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -441,3 +442,21 @@ def router_small(act32: torch.Tensor, router: torch.Tensor, logits: torch.Tensor
     _call("frb_router_small", _ptr(act32), _ptr(router), width, _ptr(logits), _ptr(_ROUTER_TICKETS[key]), _ptr(bias), tokens,
           router.shape[0], top_k, int(renormalize), float(routed_scale), tile_rows, _ptr(ids), _ptr(weights), _ptr(offsets),
           _ptr(sorted_token), _ptr(row_of_assign), _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles))
+
+
+TC_ATTENTION_HEAD_DIMS = (64, 128)
+TC_ATTENTION_QUERIES = 128
+
+
+def attention_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                         tile_seq: torch.Tensor, tile_q0: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
+                         seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
+                         num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+    """Many tokens per sequence on tcgen05 tensor cores: tiles of 128 queries of one head (bfloat16, head sizes
+    64 and 128)."""
+    for t in (q, k_pages, v_pages, out):
+        _want(t, torch.bfloat16, "tensor-core attention operands")
+    _call("frb_attention_prefill_tc", _ptr(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
+          page_table.shape[1], _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start),
+          _ptr(seq_q_len), _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0),
+          _ptr(tc_status(q.device)))

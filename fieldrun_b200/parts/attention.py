@@ -21,6 +21,9 @@ from .base import Mixer, build_position, register_part
 from .linear import linear
 
 
+TC_ATTENTION_MIN_QUERIES = 64       # a step whose longest run of new tokens is shorter uses tiles of 16 queries
+
+
 class GQAAttention(Mixer):
     replayable = True
 
@@ -104,7 +107,8 @@ class GQAAttention(Mixer):
         return linear(out, self.w_o)
 
     def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor) -> None:
-        """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128; the general kernel otherwise."""
+        """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128 (tcgen05 for prompts with head
+        sizes 64 and 128, mma.sync otherwise); the general kernel for everything else."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                       scale=self.softmax_scale, window=self.window)
         if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
@@ -114,6 +118,11 @@ class GQAAttention(Mixer):
                 part_ml = ctx.buffer("attention.part_ml", (ctx.num_seqs, self.num_heads, chunks, 2), torch.float32)
                 ops.attention_decode_mma(q, line.keys, line.values, line.page_table, ctx.seq_start, ctx.seq_slot, part_o,
                                          part_ml, out, max_chunks=chunks, **common)
+            elif self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and ctx.max_q_len >= TC_ATTENTION_MIN_QUERIES:
+                # prompts: 128 queries of one head per block, both products on tcgen05
+                tile_seq, tile_q0 = ctx.query_tiles(ops.TC_ATTENTION_QUERIES)
+                ops.attention_prefill_tc(q, line.keys, line.values, line.page_table, tile_seq, tile_q0, ctx.seq_slot,
+                                         ctx.seq_start, ctx.seq_q_len, ctx.cu_q_len, out, **common)
             else:
                 tile_seq, tile_q0 = ctx.query_tiles(16)
                 ops.attention_prefill_mma(q, line.keys, line.values, line.page_table, tile_seq, tile_q0, ctx.seq_slot,

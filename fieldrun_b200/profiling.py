@@ -6,7 +6,8 @@ profilers.
 Each case holds between a few hundred MB and 2 GB on the device (more than the L2 cache, far less than a model), runs a few
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
 arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
-``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``.
+``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``
+(mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
 this library's own.
 """
@@ -107,11 +108,19 @@ def attention(kind: str, launches: int) -> dict:
     zero = torch.zeros(1, dtype=torch.int32, device=dev)
     q_len = torch.tensor([context], dtype=torch.int32, device=dev)
     cu = torch.tensor([0, context], dtype=torch.int32, device=dev)
-    launch = lambda: ops.attention_prefill_mma(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
-                                               num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None)
+    if kind == "prefill_tc":
+        tile_seq = torch.zeros(context // 128, dtype=torch.int32, device=dev)
+        tile_q0 = torch.arange(0, context, 128, dtype=torch.int32, device=dev)
+        launch = lambda: ops.attention_prefill_tc(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
+                                                  num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None)
+    else:
+        launch = lambda: ops.attention_prefill_mma(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
+                                                   num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None)
     ms = _time(launch, launches)
+    if kind == "prefill_tc":
+        ops.tc_status_check(dev)
     flops = 4 * HEADS * HEAD_DIM * context * (context + 1) // 2
-    return {"case": "attention_prefill", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
+    return {"case": f"attention_{kind}", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
 
 
 CASES = {
@@ -119,6 +128,7 @@ CASES = {
     "experts_stream": lambda n: experts("stream", n),
     "attention_decode": lambda n: attention("decode", n),
     "attention_prefill": lambda n: attention("prefill", n),
+    "attention_prefill_tc": lambda n: attention("prefill_tc", n),
 }
 
 

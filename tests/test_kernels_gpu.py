@@ -647,3 +647,58 @@ def test_norm_adds_the_experts_outputs_in_rank_order():
     ops().rmsnorm(xd, dev(w), 1e-5, out, write_back=True, experts=(dev(y), dev(ew), dev(rowmap)))
     close(f64(xd), total, 1e-6, "stream with the experts' sum")
     close(f64(out), pm.rms_norm(total, w.astype(np.float64), 1e-5), 3e-6, "norm of it")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 1, 128, None), (4, 4, 64, None), (12, 2, 128, 100), (2, 2, 64, 70)])
+def test_many_token_attention_on_tcgen05(heads, kv_heads, head_dim, window):
+    rng = np.random.default_rng(21)
+    # (slot, tokens already in the cache, new tokens)
+    seqs = [(0, 0, 300), (2, 130, 17), (3, 0, 1), (1, 63, 200), (5, 500, 129)]
+    keys, values, table, free = paged_cache(rng, 6, 40, kv_heads, head_dim, "bfloat16")
+    keys, values = keys * 0.2, values * 0.2
+    kc, vc = f64(keys), f64(values)
+    for slot, start, n in seqs:
+        for i in range((start + n + 63) // 64):
+            table[slot, i] = free.pop()
+    positions = np.concatenate([np.arange(start, start + n) for _, start, n in seqs]).astype(np.int32)
+    slot_of = np.concatenate([np.full(n, slot) for slot, _, n in seqs]).astype(np.int32)
+    q = dev(rng.normal(size=(len(positions), heads * head_dim)), torch.bfloat16)
+    out = torch.full_like(q, 7.0)
+    tile_seq = np.concatenate([np.full((n + 127) // 128, b) for b, (_, _, n) in enumerate(seqs)]).astype(np.int32)
+    tile_q0 = np.concatenate([np.arange(0, n, 128) for _, _, n in seqs]).astype(np.int32)
+    q_lens = np.array([n for _, _, n in seqs], dtype=np.int32)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    scale = head_dim ** -0.5
+    ops().attention_prefill_tc(q, keys, values, dev(table), dev(tile_seq), dev(tile_q0),
+                               dev(np.array([s for s, _, _ in seqs], dtype=np.int32)),
+                               dev(np.array([s for _, s, _ in seqs], dtype=np.int32)), dev(q_lens), dev(cu), out,
+                               num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+    ops().tc_status_check(DEV)
+    ref = reference_attention(f64(q), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
+    close(f64(out), ref, 1e-2, "tcgen05 attention")
+
+
+def test_tcgen05_attention_finds_one_far_key_and_follows_a_late_maximum():
+    """Scores that grow from page to page force the running maximum to be raised and O to be rescaled; a single
+    far key whose score stands out must carry the output."""
+    rng = np.random.default_rng(22)
+    heads, kv_heads, head_dim, n = 2, 1, 128, 640
+    pages = n // 64
+    keys = torch.zeros(pages, kv_heads, 64, head_dim, dtype=torch.bfloat16, device=DEV)
+    values = dev(rng.normal(size=(pages, kv_heads, head_dim, 64)), torch.bfloat16)
+    table = np.arange(pages, dtype=np.int32)[::-1].copy()[None, :]
+    ramp = np.arange(n) * 0.02                                           # key j scores q . k_j = 128 * 0.5 * ramp_j * ...
+    for j in range(n):
+        keys[table[0, j // 64], 0, j % 64, :] = float(ramp[j])
+    q = dev(np.full((n, heads * head_dim), 0.25), torch.bfloat16)
+    out = torch.empty_like(q)
+    one = dev(np.array([0], dtype=np.int32))
+    tile_seq = dev(np.zeros(n // 128, dtype=np.int32))
+    tile_q0 = dev(np.arange(0, n, 128, dtype=np.int32))
+    ops().attention_prefill_tc(q, keys, values, dev(table), tile_seq, tile_q0, one, one, dev(np.array([n], dtype=np.int32)),
+                               dev(np.array([0, n], dtype=np.int32)), out, num_heads=heads, num_kv_heads=kv_heads,
+                               head_dim=head_dim, scale=1.0, window=None)
+    ops().tc_status_check(DEV)
+    positions, slot_of = np.arange(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+    ref = reference_attention(f64(q), f64(keys), f64(values), table, positions, slot_of, heads, kv_heads, head_dim, 1.0, None)
+    close(f64(out), ref, 1.5e-2, "tcgen05 attention with a rising maximum")
