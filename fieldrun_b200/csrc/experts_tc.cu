@@ -267,7 +267,10 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
     const int cols = paired ? 2 * tile_rows : tile_rows;
     p.tmem_cols = cols <= 32 ? 32 : cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
     const size_t stage_bytes = (size_t)TC_FEATS * TC_KBLOCK * 2 * (paired ? 2 : 1) + (size_t)tile_rows * TC_KBLOCK * 2;
-    int stages = (int)((200 * 1024) / stage_bytes);
+    // Two blocks per SM when both the stages (at least two each) and the accumulators fit twice: one block's
+    // set-up and epilogue then overlap the other's stream of weights.  Otherwise one block with a deeper ring.
+    const bool two_per_sm = 2 * stage_bytes <= 110 * 1024 && p.tmem_cols <= 256;
+    int stages = (int)(((two_per_sm ? 110 : 200) * 1024) / stage_bytes);
     p.stages = stages > 8 ? 8 : stages;
     const size_t smem = p.stages * stage_bytes + 1024;
     dim3 grid(max_tiles, F / TC_FEATS);
