@@ -6,7 +6,7 @@
 Prints one JSON line.  A step is one decode step of a batch of --batch sequences (default 8) whose
 prompts of 2,048 tokens were run first; `value` is decoded tokens a second with the tokens staying on the
 device, `e2e` the same through the Python entry point with host tokens in and out every step.  It also
-times a prefill of one 2,048-token prompt and decode steps at batch 1 and 64.  With --gpus above 1 it
+times a prefill of one 2,048-token prompt and decode steps at batch 1 and 64 (their prompts are run too).  With --gpus above 1 it
 says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference
 cannot run here.
 """
@@ -148,21 +148,14 @@ def main() -> int:
     def prompts(n, length):
         return [rng.integers(0, cfg.vocab_size, size=length).tolist() for _ in range(n)]
 
-    def fill(batch, real):
-        """Sequences holding PROMPT tokens each: by running the prompts, or (for the side points) by
-        reserving the pages and filling them with random keys and values."""
+    def fill(batch):
+        """Sequences holding PROMPT tokens each, by running their prompts (eight prompts a step)."""
         slots = [engine.new_sequence() for _ in range(batch)]
-        if real:
-            logits = engine.step(slots, prompts(batch, PROMPT))
-        else:
-            engine.cache.begin_step(slots, [PROMPT] * batch)
-            engine.cache.end_step(slots, [PROMPT] * batch)
-            for group in engine.cache.groups:
-                for t in (group.keys, group.values):
-                    t.normal_()
-            logits = torch.randn(batch, cfg.vocab_size, device="cuda")
         first = torch.empty(batch, dtype=torch.int32, device="cuda")
-        ops.sample_rows(logits.contiguous(), None, None, first)
+        for at in range(0, batch, 8):
+            part = slots[at:at + 8]
+            logits = engine.step(part, prompts(len(part), PROMPT))
+            ops.sample_rows(logits.contiguous(), None, None, first[at:at + len(part)])
         return slots, first
 
     def device_step(slots, tokens_dev):
@@ -207,7 +200,7 @@ def main() -> int:
     result: dict = {}
 
     # ---- the headline: decode at --batch ------------------------------------------------------------------
-    slots, first = fill(args.batch, real=True)
+    slots, first = fill(args.batch)
     timed_from = time.time()
     ms_step, launches, tokens = time_decode(slots, first, args.steps, args.warmup)
     clocks = sampler.window(timed_from, time.time())
@@ -275,7 +268,7 @@ def main() -> int:
         # ---- decode at batch 1 and 64 ------------------------------------------------------------------------
         points = {}
         for batch in (1, 64):
-            slots, first = fill(batch, real=False)
+            slots, first = fill(batch)
             ms, _, _ = time_decode(slots, first, max(8, args.steps // 2), 3)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 2)
             for s in slots:

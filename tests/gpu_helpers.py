@@ -85,3 +85,86 @@ def assert_close(got, ref, dtype: str, what: str = "", margins=None) -> None:
 @functools.lru_cache(maxsize=None)
 def loaded(name: str, dtype: str, max_tokens: int = 2048, num_slots=None):
     return fr.load(model_folder(name), dtype=dtype, max_tokens=max_tokens, num_slots=num_slots)
+
+
+# --------------------------------------------------------------------------- schedules of steps, with the experts picked
+
+class RouteRecorder:
+    """Records which experts the engine picks for every token of every step (through the feed-forward's
+    ``on_route`` hook; recorded steps are switched off meanwhile, since a replayed graph calls no hook)."""
+
+    def __init__(self, lm):
+        self.lm = lm
+        self.pending: list[np.ndarray] = []
+        self.routes: dict = {}
+
+    def __enter__(self):
+        self.was_recording = self.lm.engine.record_steps
+        self.lm.engine.record_steps = False
+        for block in self.lm.model.blocks:
+            block.feed_forward.on_route = lambda ids: self.pending.append(ids.cpu().numpy().copy())
+        return self
+
+    def __exit__(self, *exc):
+        self.lm.engine.record_steps = self.was_recording
+        for block in self.lm.model.blocks:
+            block.feed_forward.on_route = None
+        return False
+
+    def assign(self, rows):
+        """``rows``: (request, position) of every token of the step just run, in the step's order."""
+        runs, self.pending = self.pending, []
+        for run, ids in enumerate(runs):
+            for t, (key, position) in enumerate(rows):
+                self.routes.setdefault(key, {}).setdefault(run, {})[position] = ids[t]
+
+    def of(self, key, length):
+        per_run = self.routes[key]
+        return np.stack([np.stack([per_run[run][pos] for pos in range(length)]) for run in sorted(per_run)])
+
+
+def run_schedule(lm, requests, steps, recorder=None):
+    """Runs ``steps``: each a list of (request, first position, end position) whose tokens go through one
+    Engine.step with every place wanted.  A request gets a slot at its first step and gives it back after
+    the step that brings its last token.  Returns request -> logits [length, vocab]."""
+    engine = lm.engine
+    slots, rows_of = {}, {key: [] for key in requests}
+    for step in steps:
+        for key, lo, hi in step:
+            if key not in slots:
+                slots[key] = engine.new_sequence()
+        out = engine.step([slots[k] for k, _, _ in step], [requests[k][lo:hi] for k, lo, hi in step],
+                          [list(range(hi - lo)) for _, lo, hi in step]).float().cpu().numpy()
+        if recorder is not None:
+            recorder.assign([(k, pos) for k, lo, hi in step for pos in range(lo, hi)])
+        at = 0
+        for key, lo, hi in step:
+            rows_of[key].append(out[at:at + hi - lo])
+            at += hi - lo
+            if hi == len(requests[key]):
+                engine.release(slots.pop(key))
+    assert not slots, "a request of the schedule never got its last token"
+    engine.cache.check()
+    return {key: np.concatenate(parts) for key, parts in rows_of.items()}
+
+
+ROUTE_MARGIN = 5e-3     # the engine may pick another expert than the plain model only where the choice is this close
+
+
+def check_request(name, dtype, ids, logits, routes=None, what=""):
+    """float32: the logits against the plain model.  bfloat16 (``routes`` given): the logits against the plain
+    model made to pick the experts the engine picked -- a continuous function, so the full tolerance holds on
+    every row -- and the engine's picks against the plain model's own, which may differ only at near ties."""
+    config, weights = plain_weights(name)
+    if routes is None:
+        assert_close(logits, pm.logits_all_positions(config, weights, ids), dtype, what)
+        return
+    sizes = pm.sizes_from_config(config)
+    hidden, margins, own = pm.hidden_states(config, weights, ids, forced_routes=routes, return_routes=True)
+    head = weights["model.embed_tokens.weight"] if sizes["tied"] else weights["lm_head.weight"]
+    assert_close(logits, hidden @ head.astype(np.float64).T, dtype, what)
+    differs = np.sort(own, axis=-1) != np.sort(np.asarray(routes), axis=-1)
+    clear = margins > ROUTE_MARGIN
+    bad = differs.any(axis=-1) & clear
+    assert not bad.any(), (f"{what}: the engine picked other experts than the plain model at (layer, token) "
+                           f"{np.argwhere(bad)[:5].tolist()} where the margins are {margins[bad][:5]}")

@@ -155,15 +155,17 @@ def attention_layer(a, W, prefix, s, positions):
     return out @ W[prefix + "self_attn.o_proj.weight"].T
 
 
-def route(a2, router_weight, choice_bias, top_k):
+def route(a2, router_weight, choice_bias, top_k, forced_ids=None):
     """sigmoid scores; choice = score + bias; experts in descending choice, ties to the lower id (a stable
     sort); the first top_k; weights = score / sum of picked scores (src/minimax.rs:90-104).
-    Returns (ids [T, k] in rank order, weights [T, k], margin [T] between the k-th and the next choice)."""
+    Returns (ids [T, k] in rank order, weights [T, k], margin [T] between the k-th and the next choice).
+    With ``forced_ids`` the choice is given (the weights still come from the scores): this makes the model a
+    continuous function of its inputs, for comparisons that must not hinge on a near tie."""
     logits = a2 @ router_weight.T
     score = 1.0 / (1.0 + np.exp(-logits))
     choice = score + choice_bias
     order = np.argsort(-choice, axis=-1, kind="stable")
-    ids = order[:, :top_k]
+    ids = order[:, :top_k] if forced_ids is None else np.asarray(forced_ids, dtype=np.int64)
     picked = np.take_along_axis(score, ids, axis=-1)
     weights = picked / np.sum(picked, axis=-1, keepdims=True)
     ranked = np.take_along_axis(choice, order, axis=-1)
@@ -184,10 +186,11 @@ def expert_swiglu(rows, w_gate, w_up, w_down):
     return (silu(rows @ w_gate.T) * (rows @ w_up.T)) @ w_down.T
 
 
-def routed_experts(a2, W, prefix, s):
+def routed_experts(a2, W, prefix, s, forced_ids=None, return_ids=False):
     """out[t] = sum over the picked experts, in rank order, of weight * expert(a2[t]) (src/minimax.rs:88-126)."""
     moe = prefix + "block_sparse_moe."
-    ids, weights, margin = route(a2, W[moe + "gate.weight"], W[moe + "e_score_correction_bias"], s["top_k"])
+    own_ids, _, margin = route(a2, W[moe + "gate.weight"], W[moe + "e_score_correction_bias"], s["top_k"])
+    ids, weights, _ = route(a2, W[moe + "gate.weight"], W[moe + "e_score_correction_bias"], s["top_k"], forced_ids)
     out = np.zeros_like(a2)
     for t in range(a2.shape[0]):
         for rank in range(s["top_k"]):
@@ -195,6 +198,8 @@ def routed_experts(a2, W, prefix, s):
             y = expert_swiglu(a2[t:t + 1], W[f"{moe}experts.{e}.w1.weight"], W[f"{moe}experts.{e}.w3.weight"],
                               W[f"{moe}experts.{e}.w2.weight"])
             out[t] += weights[t, rank] * y[0]
+    if return_ids:
+        return out, margin, own_ids
     return out, margin
 
 
@@ -204,22 +209,27 @@ def cast_weights(W, dtype):
     return {k: (v.astype(dtype) if v.dtype.kind == "f" else v) for k, v in W.items()}
 
 
-def hidden_states(config, W, ids, dtype=np.float64, return_margins=False):
-    """All layers on a whole sequence starting at position 0, final norm included (src/minimax.rs:128-160)."""
+def hidden_states(config, W, ids, dtype=np.float64, return_margins=False, forced_routes=None, return_routes=False):
+    """All layers on a whole sequence starting at position 0, final norm included (src/minimax.rs:128-160).
+    ``forced_routes[layer]`` ([T, k] expert ids) replaces the router's choice in that layer."""
     s = sizes_from_config(config)
     W = cast_weights(W, dtype)
     positions = np.arange(len(ids))
     x = W["model.embed_tokens.weight"][np.asarray(ids, dtype=np.int64)]          # no multiplier, :132
-    margins = []
+    margins, routes = [], []
     for layer in range(s["layers"]):
         p = f"model.layers.{layer}."
         a = rms_norm(x, W[p + "input_layernorm.weight"], s["eps"])
         x = x + attention_layer(a, W, p, s, positions)
         a2 = rms_norm(x, W[p + "post_attention_layernorm.weight"], s["eps"])
-        y, margin = routed_experts(a2, W, p, s)
+        forced = None if forced_routes is None else forced_routes[layer]
+        y, margin, own = routed_experts(a2, W, p, s, forced, return_ids=True)
         margins.append(margin)
+        routes.append(own)
         x = x + y
     out = rms_norm(x, W["model.norm.weight"], s["eps"])
+    if return_routes:
+        return out, np.stack(margins), np.stack(routes)
     return (out, np.stack(margins)) if return_margins else out
 
 

@@ -76,3 +76,20 @@ def test_plan_is_data():
     ff = plan.layers[2].feed_forward
     assert ff.kind == "routed_experts" and ff.args["top_k"] == 3 and ff.args["choice_bias"]
     assert ff.tensors["w_down"] == "model.layers.2.block_sparse_moe.experts.{e}.w2.weight"
+
+
+def test_rotary_tables_are_the_reference_angles():
+    """cos/sin of pos * theta^(-2j/rotary_dim) (src/minimax.rs:50,76), to float32 rounding."""
+    import numpy as np
+    from fieldrun_b200.parts.position import Rotary
+    cos, sin = Rotary({"rotary_dim": 12, "theta": 5000000.0}).tables(300, "cpu")
+    assert cos.shape == (300, 6) and cos.dtype.is_floating_point
+    pos, j = np.arange(300)[:, None], np.arange(6)[None, :]
+    angle = pos * (1.0 / 5000000.0 ** (2.0 * j / 12))
+    np.testing.assert_allclose(cos.numpy(), np.cos(angle), atol=1e-7)
+    np.testing.assert_allclose(sin.numpy(), np.sin(angle), atol=1e-7)
+    scaled, _ = Rotary({"rotary_dim": 12, "theta": 5000000.0, "position_scale": 0.5}).tables(300, "cpu")
+    np.testing.assert_allclose(scaled.numpy()[2 * np.arange(100)], cos.numpy()[:100], atol=1e-7)
+    assert Rotary({"rotary_dim": 0, "theta": 1.0}).tables(10, "cpu") == (None, None)
+    with pytest.raises(ValueError, match="even"):
+        Rotary({"rotary_dim": 5, "theta": 1.0})

@@ -5,8 +5,8 @@ import pytest
 import torch
 
 import plain_model as pm
-from gpu_helpers import (TOLERANCE, assert_close, loaded, model_folder, plain_logits, plain_margins, plain_weights,
-                         request_tokens, worst)
+from gpu_helpers import (TOLERANCE, RouteRecorder, assert_close, check_request, loaded, model_folder, plain_logits,
+                         plain_margins, plain_weights, request_tokens, run_schedule, worst)
 from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
@@ -20,16 +20,25 @@ def to_np(t):
     return t.float().cpu().numpy()
 
 
+def run_and_check(name, dtype, lm, requests, steps, what):
+    """Runs the schedule and compares every request with the plain model (see gpu_helpers.check_request)."""
+    if dtype == "bfloat16":
+        with RouteRecorder(lm) as recorder:
+            logits = run_schedule(lm, requests, steps, recorder)
+        for key, ids in requests.items():
+            check_request(name, dtype, ids, logits[key], recorder.of(key, len(ids)), f"{name} {what}, request {key}")
+    else:
+        logits = run_schedule(lm, requests, steps)
+        for key, ids in requests.items():
+            check_request(name, dtype, ids, logits[key], None, f"{name} {what}, request {key}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_each_request_alone_and_whole(name, dtype):
     lm = loaded(name, dtype)
-    for length in LENGTHS:
-        ids = request_tokens(name, length, 0)
-        got = to_np(lm.logits(ids))
-        assert_close(got, plain_logits(name, length, 0), dtype, f"{name} whole request of {length}",
-                     plain_margins(name, length, 0))
-    lm.engine.cache.check()
+    requests = {n: request_tokens(name, n, 0) for n in LENGTHS + [300]}
+    run_and_check(name, dtype, lm, requests, [[(n, 0, n)] for n in requests], "whole")
     assert lm.engine.cache.slots.num_held == 0
 
 
@@ -37,20 +46,12 @@ def test_each_request_alone_and_whole(name, dtype):
 @pytest.mark.parametrize("name", NAMES)
 def test_last_32_tokens_one_by_one(name, dtype):
     lm = loaded(name, dtype)
-    engine = lm.engine
-    for length in (40, 77, 130):
-        ids = request_tokens(name, length, 0)
-        ref = plain_logits(name, length, 0)
-        head = length - 32
-        slot = engine.new_sequence()
-        try:
-            rows = [to_np(engine.step([slot], [ids[:head]], [list(range(head))]))]
-            for i in range(head, length):
-                rows.append(to_np(engine.step([slot], [[ids[i]]], [[0]])))
-        finally:
-            engine.release(slot)
-        assert_close(np.concatenate(rows), ref, dtype, f"{name} length {length}, last 32 one by one",
-                     plain_margins(name, length, 0))
+    requests = {n: request_tokens(name, n, 0) for n in (40, 77, 130)}
+    steps = []
+    for n in requests:
+        steps.append([(n, 0, n - 32)])
+        steps.extend([[(n, j, j + 1)] for j in range(n - 32, n)])
+    run_and_check(name, dtype, lm, requests, steps, "last 32 one by one")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -59,36 +60,35 @@ def test_unequal_batches_through_few_slots(name, dtype):
     """Three slots, seven requests: prompts of a batch in one step, then one token each, the shorter
     ones leaving earlier; the next batch takes the freed slots."""
     lm = loaded(name, dtype, 2048, 3)
-    engine = lm.engine
     plan = [(130, 9), (5, 2), (77, 20), (1, 0), (64, 33), (40, 39), (13, 5)]      # (length, decoded at the end)
+    requests = {n: request_tokens(name, n, 0) for n, _ in plan}
+    steps = []
     for start in range(0, len(plan), 3):
         batch = plan[start:start + 3]
-        slots = [engine.new_sequence() for _ in batch]
-        ids = [request_tokens(name, length, 0) for length, _ in batch]
-        got = [[] for _ in batch]
-        heads = [length - dec for length, dec in batch]
-        out = to_np(engine.step(slots, [i[:h] for i, h in zip(ids, heads)], [list(range(h)) for h in heads]))
-        at = 0
-        for b, h in enumerate(heads):
-            got[b].append(out[at:at + h])
-            at += h
-        step = 0
-        while True:
-            live = [b for b, (length, dec) in enumerate(batch) if step < dec]
-            if not live:
-                break
-            out = to_np(engine.step([slots[b] for b in live], [[ids[b][heads[b] + step]] for b in live]))
-            for row, b in enumerate(live):
-                got[b].append(out[row:row + 1])
-            step += 1
-        for slot in slots:
-            engine.release(slot)
-        engine.cache.check()
-        for b, (length, dec) in enumerate(batch):
-            assert_close(np.concatenate(got[b]), plain_logits(name, length, 0), dtype,
-                         f"{name} batch at {start}, request of {length} with {dec} decoded",
-                         plain_margins(name, length, 0))
-    assert engine.cache.slots.num_held == 0
+        steps.append([(n, 0, n - dec) for n, dec in batch])
+        for k in range(max(dec for _, dec in batch)):
+            steps.append([(n, n - dec + k, n - dec + k + 1) for n, dec in batch if k < dec])
+    run_and_check(name, dtype, lm, requests, steps, "unequal batches")
+    assert lm.engine.cache.slots.num_held == 0
+
+
+@pytest.mark.parametrize("name", ["a", "d"])
+def test_recorded_steps_in_bfloat16(name):
+    """The same decode steps replayed from their recording and run directly: the same logits, bit for bit."""
+    lm = loaded(name, "bfloat16")
+    requests = {n: request_tokens(name, n, 5) for n in (70, 9, 33)}
+    steps = [[(n, 0, n - 8) for n in requests]] + [[(n, n - 8 + k, n - 7 + k) for n in requests] for k in range(8)]
+    lm.engine.record_steps = True
+    before = lm.engine.steps_replayed
+    replayed = run_schedule(lm, requests, steps)
+    assert lm.engine.steps_replayed >= before + 6
+    lm.engine.record_steps = False
+    try:
+        direct = run_schedule(lm, requests, steps)
+    finally:
+        lm.engine.record_steps = True
+    for n in requests:
+        np.testing.assert_array_equal(replayed[n], direct[n])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

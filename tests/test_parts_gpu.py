@@ -431,3 +431,24 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
         for r, got in zip(batch, rows):
             close(np.concatenate(got), plain(r), 1e-5, f"toy mixer, request of {len(r)}")
     engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_and_head_parts(dtype):
+    _, config, _, parts, _ = lib()
+    rng = np.random.default_rng(6)
+    table = rng.normal(size=(97, 40))
+    emb = parts.build_part("embedding", config.PartSpec("token_embedding", {"vocab_size": 97, "width": 40}, {"weight": "e"}), TORCH[dtype])
+    head = parts.build_part("head", config.PartSpec("vocab_head", {"vocab_size": 97, "width": 40}, {"weight": "e"}), TORCH[dtype])
+    emb.load(source({"e": table}, dtype))
+    head.load(source({"e": table}, dtype), shared=emb.weight)            # a tied head uses the embedding's tensor
+    assert head.weight.data_ptr() == emb.weight.data_ptr()
+    held = rounded({"e": table}, ["e"], dtype)["e"]
+    stepper = Stepper([], dtype)
+    ctx = stepper.engine.StepContext(stepper.workspace, TORCH[dtype], [0], [0], [6])
+    tokens = torch.tensor([3, 96, 0, 3, 50, 7], dtype=torch.int32, device=DEV)
+    x = emb.forward(ctx, tokens)
+    assert x.dtype == torch.float32
+    np.testing.assert_array_equal(f64(x), held[[3, 96, 0, 3, 50, 7]])
+    rows = x.to(TORCH[dtype])
+    close(f64(head.forward(ctx, rows)), f64(rows) @ held.T, 1e-5 if dtype == "float32" else 1e-2, "head")

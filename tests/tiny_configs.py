@@ -29,4 +29,12 @@ CONFIG_C = dict(
     tie_word_embeddings=True)
 INIT_C = RandomInit(seed=2, matrix_std=0.05, norm_std=0.2, bias_std=0.05, stored_dtype=torch.float32)
 
-ALL = {"a": (CONFIG_A, INIT_A), "b": (CONFIG_B, INIT_B), "c": (CONFIG_C, INIT_C)}
+# sizes that the tcgen05 kernels take (widths in steps of 128, head size 64), so that prompts of a few dozen
+# tokens run on them inside the engine
+CONFIG_D = dict(
+    architectures=[ARCH], model_type="minimax_m2", num_hidden_layers=2, hidden_size=128, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=64, rotary_dim=32, rope_theta=50000.0, use_qk_norm=True, num_local_experts=4,
+    num_experts_per_tok=2, intermediate_size=128, vocab_size=300, rms_norm_eps=1e-6, tie_word_embeddings=False)
+INIT_D = RandomInit(seed=3, matrix_std=0.04, norm_std=0.1, bias_std=0.05)
+
+ALL = {"a": (CONFIG_A, INIT_A), "b": (CONFIG_B, INIT_B), "c": (CONFIG_C, INIT_C), "d": (CONFIG_D, INIT_D)}
