@@ -197,3 +197,54 @@ def test_errors_come_before_any_launch():
     finally:
         engine.release(slot)
     engine.cache.check()
+
+
+def test_a_long_request_over_many_pages_and_key_chunks():
+    """2,500 tokens as a prompt, then 60 more one by one: forty pages, ten key chunks per decode step, the
+    chunks' partial results merged in order."""
+    name, dtype = "b", "bfloat16"
+    lm = loaded(name, dtype, 4096, 2)
+    n = 2560
+    requests = {"long": request_tokens(name, n, 9)}
+    steps = [[("long", 0, 2500)]] + [[("long", j, j + 1)] for j in range(2500, n)]
+    with RouteRecorder(lm) as recorder:
+        logits = run_schedule(lm, requests, steps, recorder)
+    # the plain model on 2,560 tokens is slow: compare the prompt's last rows and every decoded row
+    config, weights = plain_weights(name)
+    sizes = pm.sizes_from_config(config)
+    hidden = pm.hidden_states(config, weights, requests["long"], forced_routes=recorder.of("long", n))
+    ref = hidden[2400:] @ weights["lm_head.weight"].astype(np.float64).T
+    assert_close(logits["long"][2400:], ref, dtype, "a request of 2,560 tokens")
+    assert sizes["layers"] == 3
+
+
+M2_SHAPED = dict(
+    architectures=["MiniMaxM2ForCausalLM"], model_type="minimax_m2", num_hidden_layers=1, hidden_size=3072,
+    num_attention_heads=48, num_key_value_heads=8, head_dim=128, rotary_dim=64, rope_theta=5000000.0, use_qk_norm=True,
+    num_local_experts=16, num_experts_per_tok=8, intermediate_size=1536, vocab_size=2003, rms_norm_eps=1e-6,
+    tie_word_embeddings=False)
+
+
+def test_a_layer_of_minimax_m2_size():
+    """One layer with MiniMax-M2's own sizes (48 heads over 8, head size 128 with 64 rotary dims, q/k norms
+    6,144 and 1,024 wide, experts 3,072 x 1,536, top 8; fewer experts and a small vocabulary keep the folder
+    small): a prompt long enough for the tcgen05 kernels, then decode steps on the streaming kernels."""
+    import tempfile
+
+    import fieldrun_b200 as fr
+    with tempfile.TemporaryDirectory() as folder:
+        fr.write_random_model(folder, M2_SHAPED, fr.RandomInit(seed=4, matrix_std=0.02, norm_std=0.1, bias_std=0.01))
+        config, weights = pm.read_model_folder(folder)
+        lm = fr.load(folder, dtype="bfloat16", max_tokens=512)
+        ids = np.random.default_rng(11).integers(0, 2003, size=76).tolist()
+        requests = {"r": ids, "s": ids[5:30]}
+        steps = [[("r", 0, 70), ("s", 0, 20)]] + [[("r", 70 + k, 71 + k)] + ([("s", 20 + k, 21 + k)] if k < 5 else []) for k in range(6)]
+        with RouteRecorder(lm) as recorder:
+            logits = run_schedule(lm, requests, steps, recorder)
+        for key, tokens in requests.items():
+            routes = recorder.of(key, len(tokens))
+            hidden, margins, own = pm.hidden_states(config, weights, tokens, forced_routes=routes, return_routes=True)
+            ref = hidden @ weights["lm_head.weight"].astype(np.float64).T
+            assert_close(logits[key], ref, "bfloat16", f"MiniMax-M2-sized layer, request {key}")
+            differs = (np.sort(own, axis=-1) != np.sort(routes, axis=-1)).any(axis=-1)
+            assert not (differs & (margins > 5e-3)).any()
