@@ -153,58 +153,73 @@ struct QkvParams {
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
 };
 
-template <typename WT>
-__device__ __forceinline__ float normed(const float* raw, const WT* w, float rinv, int i) {
-    return w ? raw[i] * rinv * to_f32<WT>(w[i]) : raw[i];
-}
+#define QKV_BATCH 8          // elements a thread loads before it uses any of them
 
-// One block per token.  The raw Q and K rows sit in shared memory; each thread produces output elements
-// from the raw values of its own element and of its rotation partner.
+// One block per token.  A thread first issues all of its loads (a batch of raw values with their norm
+// weights), so that their latencies overlap; the rows then sit in shared memory, Q and K already multiplied
+// by their weights, and each thread produces output elements from its own element and its rotation partner.
 template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
-    extern __shared__ float raw[];           // [(nh + nkv) * hd] : Q row then K row
+    extern __shared__ float raw[];           // [(nh + 2 nkv) * hd] : Q row, K row, V row; then cos and sin [rotary_dim / 2]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
-    const InT* src = (const InT*)p.qkv + (size_t)t * (q_width + 2 * k_width);
-    float ssq = 0.f, ssk = 0.f;
-    for (int i = threadIdx.x; i < q_width + k_width; i += NORM_BLOCK) {
-        const float v = to_f32<InT>(src[i]);
-        raw[i] = v;
-        if (i < q_width) ssq += v * v; else ssk += v * v;
-    }
+    const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    const int half = p.rotary_dim / 2;
+    float* s_cos = raw + all_width;
+    float* s_sin = s_cos + half;
+    const InT* src = (const InT*)p.qkv + (size_t)t * all_width;
     const WT* qw = (const WT*)p.q_weight;
     const WT* kw = (const WT*)p.k_weight;
+
+    const int pos = p.tok_pos[t];
+    const int slot = p.tok_slot[t];
+    float ssq = 0.f, ssk = 0.f;
+    for (int base = 0; base < all_width; base += QKV_BATCH * NORM_BLOCK) {
+        float v[QKV_BATCH], w[QKV_BATCH];
+#pragma unroll
+        for (int u = 0; u < QKV_BATCH; ++u) {
+            const int i = base + u * NORM_BLOCK + threadIdx.x;
+            v[u] = i < all_width ? to_f32<InT>(src[i]) : 0.f;
+            w[u] = 1.f;
+            if (i < q_width) { if (qw) w[u] = to_f32<WT>(qw[i]); }
+            else if (i < qk_width) { if (kw) w[u] = to_f32<WT>(kw[i - q_width]); }
+        }
+#pragma unroll
+        for (int u = 0; u < QKV_BATCH; ++u) {
+            const int i = base + u * NORM_BLOCK + threadIdx.x;
+            if (i < all_width) raw[i] = v[u] * w[u];
+            if (i < q_width) ssq += v[u] * v[u];
+            else if (i < qk_width) ssk += v[u] * v[u];
+        }
+    }
+    const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
+    for (int j = threadIdx.x; j < half; j += NORM_BLOCK) {
+        s_cos[j] = p.cos_table[(size_t)table_row * half + j];
+        s_sin[j] = p.sin_table[(size_t)table_row * half + j];
+    }
+    const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
+    const int in_page = pos % FRB_PAGE;
     float rinv_q = 1.f, rinv_k = 1.f;
     if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
     if (kw) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
     __syncthreads();
 
-    const int pos = p.tok_pos[t];
-    const int slot = p.tok_slot[t];
-    const int half = p.rotary_dim / 2;
-    const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
-    const float* cs = p.cos_table + (size_t)table_row * half;
-    const float* sn = p.sin_table + (size_t)table_row * half;
-    const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
-    const int in_page = pos % FRB_PAGE;
-
-    for (int i = threadIdx.x; i < q_width + k_width; i += NORM_BLOCK) {
+    for (int i = threadIdx.x; i < qk_width; i += NORM_BLOCK) {
         const bool is_q = i < q_width;
         const float* base = is_q ? raw : raw + q_width;
-        const WT* w = is_q ? qw : kw;
         const float rinv = is_q ? rinv_q : rinv_k;
         const int local = is_q ? i : i - q_width;
-        const int head = local / hd, dim = local % hd;
-        float value = normed<WT>(base, w, rinv, local);
+        const int head = local / hd, dim = local - head * hd;
+        float value = base[local] * rinv;
         if (dim < p.rotary_dim) {
             int j, partner;
             bool first;
             if (p.interleaved) { j = dim >> 1; first = (dim & 1) == 0; partner = first ? local + 1 : local - 1; }
             else { first = dim < half; j = first ? dim : dim - half; partner = first ? local + half : local - half; }
-            const float other = normed<WT>(base, w, rinv, partner);
-            const float c = cs[j], s = sn[j];
+            const float other = base[partner] * rinv;
+            const float c = s_cos[j], s = s_sin[j];
             // a' = a c - b s ; b' = b c + a s   (src/minimax.rs:78-81)
             value = first ? value * c - other * s : value * c + other * s;
         }
@@ -216,11 +231,11 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
         }
     }
     if (page >= 0) {
-        const InT* vsrc = src + q_width + k_width;
+        const float* vrow = raw + qk_width;
         for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
-            const int head = i / hd, dim = i % hd;
+            const int head = i / hd, dim = i - head * hd;
             const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
-            ((OutT*)p.v_pages)[at] = from_f32<OutT>(to_f32<InT>(vsrc[i]));
+            ((OutT*)p.v_pages)[at] = from_f32<OutT>(vrow[i]);
         }
     }
 }
@@ -241,9 +256,9 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.v_pages = v_pages; p.eps = eps; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
     p.rotary_dim = rotary_dim; p.interleaved = interleaved; p.max_pages = max_pages; p.write_cache = write_cache;
     p.table_positions = table_positions;
-    const size_t smem = (size_t)(num_heads + num_kv_heads) * head_dim * sizeof(float);
-    FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + kv heads) * head_dim = %d needs more than 200 KB of shared memory",
-                  (num_heads + num_kv_heads) * head_dim);
+    const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim) * sizeof(float);
+    FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + 2 kv heads) * head_dim = %d needs more than 200 KB of shared memory",
+                  (num_heads + 2 * num_kv_heads) * head_dim);
     FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
         if (num_tokens <= NORM_FEW_ROWS) {
             auto kernel = qkv_prepare_kernel<InT, OutT, WT, 1024>;

@@ -352,6 +352,7 @@ def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Ten
 
 
 SMALL_ROUTE_ASSIGNMENTS = 1024
+SMALL_ROUTE_TOKENS = 16       # one token per warp of the one-block kernel: beyond that the separate kernels are faster
 ROUTER_SMALL_TOKENS = 8       # most tokens of a step for router_small
 
 

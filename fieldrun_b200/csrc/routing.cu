@@ -9,17 +9,78 @@
 
 // ----------------------------------------------------------------------------- top-k choice
 
+// Floats as unsigned integers in the same order (so that the warp's maximum is one redux instruction).
+__device__ __forceinline__ unsigned int ordered_bits(float v) {
+    const unsigned int u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+#define PICK_PER_LANE 8      // experts a lane keeps in registers: up to 256 experts on the fast path
+
 // One warp picks one token's experts.  z: the token's E logits; score/choice: E floats of scratch each.
+// Each lane owns the experts lane, lane + 32, ...; a round finds the largest choice value in the warp (ties:
+// the lowest expert id, as a stable sort would), hands it out and removes it.
 __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const float* __restrict__ bias, int num_experts,
                                              int top_k, int renormalize, float routed_scale, float* score, float* choice,
                                              int* __restrict__ ids, float* __restrict__ weights, int lane) {
+    float denom = 0.f;
+    if (num_experts <= 32 * PICK_PER_LANE && top_k <= 32) {
+        // the lane's candidates stay in registers; NaN scores count as the smallest value
+        float mine[PICK_PER_LANE], sc[PICK_PER_LANE];
+#pragma unroll
+        for (int i = 0; i < PICK_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < num_experts) {
+                const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));   // read through L2: another block may have written it
+                sc[i] = s;
+                const float c = bias ? s + bias[e] : s;
+                mine[i] = c == c ? c : -INFINITY;
+            } else {
+                sc[i] = 0.f;
+                mine[i] = -INFINITY;
+            }
+        }
+        unsigned int taken = 0;                         // bit i: this lane's candidate i is handed out (or absent)
+#pragma unroll
+        for (int i = 0; i < PICK_PER_LANE; ++i)
+            if (lane + 32 * i >= num_experts) taken |= 1u << i;
+        float picked_score = 0.f;                       // lane r keeps the score of the rank-r pick
+        int picked_id = 0;
+        for (int r = 0; r < top_k; ++r) {
+            float best = -INFINITY;
+            int best_i = -1;
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (!(taken & (1u << i)) && (best_i < 0 || mine[i] > best)) { best = mine[i]; best_i = i; }
+            const unsigned int key = best_i >= 0 ? ordered_bits(best) : 0u;
+            const unsigned int top = __reduce_max_sync(0xffffffffu, key);
+            const int my_e = (best_i >= 0 && key == top) ? lane + 32 * best_i : 0x7fffffff;
+            const int e = __reduce_min_sync(0xffffffffu, my_e);          // the lowest id among equal values
+            const int owner = e & 31, slot = e >> 5;
+            float s_e = 0.f;
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (i == slot) s_e = sc[i];
+            s_e = __shfl_sync(0xffffffffu, s_e, owner);
+            if (lane == owner) taken |= 1u << slot;
+            if (lane == r) { picked_score = s_e; picked_id = e; }
+            denom += s_e;
+        }
+        if (lane < top_k) {
+            float w = picked_score;
+            if (renormalize) w = w / denom;               // s_e / sum of picked s (src/minimax.rs:100-103)
+            ids[lane] = picked_id;
+            weights[lane] = w * routed_scale;
+        }
+        __syncwarp();
+        return;
+    }
     for (int e = lane; e < num_experts; e += 32) {
-        const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));      // read through L2: another block may have written it
+        const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));
         score[e] = s;
         choice[e] = bias ? s + bias[e] : s;
     }
     __syncwarp();
-    float denom = 0.f;
     for (int r = 0; r < top_k; ++r) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -275,14 +336,25 @@ __device__ __forceinline__ void route_and_plan(const SmallRouteParams& p, float*
             p.tile_expert[tile] = e;
             p.tile_row0[tile] = first[e] + r;
         }
-        int at = first[e];
-        if (count[e] > 0) {
-            for (int a = 0; a < num_assign; ++a) {
-                if (s_ids[a] == e) {
-                    p.sorted_token[at] = a / top_k;
-                    p.row_of_assign[a] = at;
-                    ++at;
-                }
+    }
+    __syncthreads();                                                     // first[] is read above and moved below
+    if (warp == 0) {
+        // one warp walks the assignments 32 at a time, in order: lanes with the same expert find one another
+        // with a match and take consecutive places behind the expert's earlier rows (first[] moves on)
+        for (int base = 0; base < num_assign; base += 32) {
+            const int a = base + lane;
+            const bool live = a < num_assign;
+            const int e = live ? s_ids[a] : -1 - lane;
+            const unsigned same = __match_any_sync(0xffffffffu, e);
+            const int rank = __popc(same & ((1u << lane) - 1));
+            int at = 0;
+            if (live) at = first[e] + rank;
+            __syncwarp();
+            if (live && rank == 0) first[e] += __popc(same);
+            __syncwarp();
+            if (live) {
+                p.sorted_token[at] = a / top_k;
+                p.row_of_assign[a] = at;
             }
         }
     }

@@ -202,7 +202,8 @@ class RoutedExperts(FeedForward):
     def forward_deferred(self, ctx, act, act32):
         if act32 is None:
             raise ValueError("routed experts need the normed rows in float32 for the router")
-        if act.shape[0] * self.top_k <= ops.SMALL_ROUTE_ASSIGNMENTS and self.num_experts <= 1024:
+        if (act.shape[0] <= ops.SMALL_ROUTE_TOKENS and act.shape[0] * self.top_k <= ops.SMALL_ROUTE_ASSIGNMENTS
+                and self.num_experts <= 1024):
             ids, weights, p = self.route_and_plan(ctx, act32)
             if self.on_route is not None:
                 self.on_route(ids)

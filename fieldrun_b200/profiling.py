@@ -37,6 +37,25 @@ def _time(launch, launches: int, warmup: int = 3) -> float:
     return begin.elapsed_time(end) / launches
 
 
+def _time_recorded(launch, launches: int) -> float:
+    """Milliseconds per launch with the launches recorded into one CUDA graph, so that the host's cost of a
+    call (several microseconds from Python) is not what is measured."""
+    launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(launches):
+            launch()
+    graph.replay()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / launches
+
+
 def _expert_lists(rows_per_expert: list[int], tile_rows: int, device):
     offsets = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
     tiles = [(e, offsets[e] + r) for e, n in enumerate(rows_per_expert) for r in range(0, n, tile_rows)]
@@ -123,12 +142,54 @@ def attention(kind: str, launches: int) -> dict:
     return {"case": f"attention_{kind}", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
 
 
+def small_kernels(launches: int) -> dict:
+    """The latency-bound kernels of a decode step of 8 sequences, each launched back to back."""
+    dev = torch.device("cuda")
+    launches = max(launches, 200)            # a replay's own cost, spread over few launches, would show in each
+    tokens, experts_n, top_k = 8, 256, 8
+    out = {"case": "decode_small_kernels", "tokens": tokens}
+    x = torch.randn(tokens, HIDDEN, device=dev)
+    delta = torch.randn(tokens, HIDDEN, device=dev)
+    weight = torch.ones(HIDDEN, device=dev)
+    act = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev)
+    act32 = torch.empty(tokens, HIDDEN, device=dev)
+    out["rmsnorm_us"] = round(1000 * _time_recorded(lambda: ops.rmsnorm(x, weight, 1e-6, act, delta=delta, out32=act32, write_back=True), launches), 2)
+    router = torch.randn(experts_n, HIDDEN, device=dev) * 0.02
+    bias = torch.zeros(experts_n, device=dev)
+    n = tokens * top_k
+    i32 = lambda k: torch.zeros(k, dtype=torch.int32, device=dev)
+    ids, weights = torch.zeros(tokens, top_k, dtype=torch.int32, device=dev), torch.zeros(tokens, top_k, device=dev)
+    lists = [i32(experts_n + 1), i32(n), i32(n), i32(n + experts_n), i32(n + experts_n), i32(1)]
+    logits = torch.empty(tokens, experts_n, device=dev)
+    out["router_small_us"] = round(1000 * _time_recorded(lambda: ops.router_small(act32, router, logits, bias, top_k, True, 1.0, 8, ids, weights, *lists), launches), 2)
+    out["route_plan_small_us"] = round(1000 * _time_recorded(lambda: ops.route_plan_small(logits, bias, top_k, True, 1.0, 8, ids, weights, *lists), launches), 2)
+    qkv = torch.randn(tokens, (HEADS + 2 * KV_HEADS) * HEAD_DIM, device=dev)
+    qw, kw = torch.ones(HEADS * HEAD_DIM, device=dev), torch.ones(KV_HEADS * HEAD_DIM, device=dev)
+    cos, sin = torch.ones(4096, 32, device=dev), torch.zeros(4096, 32, device=dev)
+    pos = torch.full((tokens,), 3000, dtype=torch.int32, device=dev)
+    slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+    pages = tokens * 64
+    keys = torch.zeros(pages, KV_HEADS, 64, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    values = torch.zeros(pages, KV_HEADS, HEAD_DIM, 64, dtype=torch.bfloat16, device=dev)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(tokens, 64).contiguous()
+    q = torch.empty(tokens, HEADS * HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    out["qkv_prepare_us"] = round(1000 * _time_recorded(lambda: ops.qkv_prepare(qkv, qw, kw, 1e-6, cos, sin, pos, slots, table, q, keys, values,
+                                                                       num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, rotary_dim=64,
+                                                                       interleaved=False, write_cache=True), launches), 2)
+    y = torch.randn(n, HIDDEN, device=dev)
+    rowmap = torch.arange(n, dtype=torch.int32, device=dev)
+    out["rmsnorm_with_experts_us"] = round(1000 * _time_recorded(lambda: ops.rmsnorm(x, weight, 1e-6, act, out32=act32, write_back=True,
+                                                                            experts=(y, weights.abs() + 0.1, rowmap)), launches), 2)
+    return out
+
+
 CASES = {
     "experts_tc": lambda n: experts("tc", n),
     "experts_stream": lambda n: experts("stream", n),
     "attention_decode": lambda n: attention("decode", n),
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
+    "decode_small_kernels": small_kernels,
 }
 
 
