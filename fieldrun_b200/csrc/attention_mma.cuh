@@ -193,6 +193,7 @@ struct DecodeAttnParams {
 // four warps' results are combined through shared memory.
 template <int HD>
 __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttnParams p) {
+    after_previous_kernel();
     __shared__ float sm_o[4][16][HD + 8];
     __shared__ float sm_m[4][16], sm_l[4][16];
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -319,6 +320,7 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
 // grid (head, sequence): merges the chunks of one (sequence, head), first chunk to last.
 template <int HD>
 __global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnParams p) {
+    after_previous_kernel();
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int pos = p.seq_pos[b];
     const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
@@ -355,8 +357,8 @@ static inline int launch_attention_decode(const char* what, const void* q, const
     p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks;
     dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
 #define FRB_LAUNCH_DECODE(HD)                                                       \
-    attention_decode_mma_kernel<HD><<<grid, 128, 0, stream>>>(p);                   \
-    attention_decode_merge_kernel<HD><<<merge_grid, HD, 0, stream>>>(p)
+    launch_dependent(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), 0, stream, p);                   \
+    launch_dependent(attention_decode_merge_kernel<HD>, dim3(merge_grid), dim3(HD), 0, stream, p)
     if (head_dim == 32) { FRB_LAUNCH_DECODE(32); } else if (head_dim == 64) { FRB_LAUNCH_DECODE(64); }
     else if (head_dim == 96) { FRB_LAUNCH_DECODE(96); } else { FRB_LAUNCH_DECODE(128); }
 #undef FRB_LAUNCH_DECODE

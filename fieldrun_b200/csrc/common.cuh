@@ -4,6 +4,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -36,6 +37,49 @@ void frb_set_error(const char* fmt, ...);
         }                                                                         \
         return 0;                                                                 \
     } while (0)
+
+// Programmatic dependent launch.  A kernel started with launch_dependent() may begin while the kernel before
+// it in the stream still runs; it calls after_previous_kernel() before it reads or writes anything, which
+// first lets the kernel after it begin in the same way and then waits until the kernel before it has ended
+// and its writes are visible.  What the launch hides is the time between one kernel's last block and the next
+// kernel's first instruction, which is most of the cost of the small kernels of a decode step.  In a kernel
+// that was started in the ordinary way both instructions do nothing.
+__device__ __forceinline__ void after_previous_kernel() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// The largest grid that is started early: the number of SMs, or FIELDRUN_B200_PDL from the environment
+// (0 starts every kernel in the ordinary way).  Blocks that start early settle on whichever SMs have room at
+// that moment; a kernel of many blocks that is bound by memory bandwidth then runs from an uneven placement
+// and loses more than the early start gains, so only the small kernels are started early.
+inline long frb_dependent_launch_blocks() {
+    static const long most = [] {
+        const char* v = getenv("FIELDRUN_B200_PDL");
+        if (v && v[0]) return atol(v);
+        int device = 0, sms = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        return (long)sms;
+    }();
+    return most;
+}
+
+// Starts `kernel`, whose first statement is after_previous_kernel().
+template <typename... Params, typename... Args>
+inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = (long)grid.x * grid.y * grid.z <= frb_dependent_launch_blocks() ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -28,6 +28,7 @@ FRB_API int frb_abi_version() { return 3; }
 template <typename WT>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const WT* __restrict__ table, float* __restrict__ out,
                                   int width, int vocab) {
+    after_previous_kernel();
     const int t = blockIdx.x;
     int token = tokens[t];
     if (token < 0 || token >= vocab) token = 0;      // ids are checked on the host before any launch
@@ -41,7 +42,7 @@ FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype
                            int width, int vocab, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     FRB_DISPATCH_DTYPE(table_dtype, WT, {
-        embed_rows_kernel<WT><<<num_tokens, 256, 0, stream>>>(tokens, (const WT*)table, out, width, vocab);
+        launch_dependent(embed_rows_kernel<WT>, dim3(num_tokens), dim3(256), 0, stream, tokens, (const WT*)table, out, width, vocab);
     });
     FRB_RETURN_LAUNCH("embed_rows");
 }
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(NORM_BLOCK)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum experts, const int* __restrict__ rows,
                const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
                int write_back) {
+    after_previous_kernel();
     extern __shared__ float row[];
     __shared__ float scratch[32];
     __shared__ float expert_weight[NORM_MAX_TOP_K];
@@ -123,12 +125,12 @@ FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, con
         if (num_rows <= NORM_FEW_ROWS) {
             auto kernel = rmsnorm_kernel<OutT, WT, 1024>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<num_rows, 1024, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
+            launch_dependent(kernel, dim3(num_rows), dim3(1024), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
                                                      write_back);
         } else {
             auto kernel = rmsnorm_kernel<OutT, WT, 256>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<num_rows, 256, smem, stream>>>(x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
+            launch_dependent(kernel, dim3(num_rows), dim3(256), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
                                                     write_back);
         }
     }));
@@ -160,6 +162,7 @@ struct QkvParams {
 // by their weights, and each thread produces output elements from its own element and its rotation partner.
 template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
+    after_previous_kernel();
     extern __shared__ float raw[];           // [(nh + 2 nkv) * hd] : Q row, K row, V row; then cos and sin [rotary_dim / 2]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
@@ -240,6 +243,120 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     }
 }
 
+// Four neighbouring elements at once.
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned int*>(&lo);
+    raw.y = *reinterpret_cast<const unsigned int*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+#define QKV_VEC_BATCH 4      // groups of four elements a thread loads before it uses any of them
+
+// The same work four elements at a time, for head sizes and rotation widths in steps of four (eight for the
+// half-split pairing, so that a group's partners are a group too) and rows that start on 16 bytes.
+template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
+__global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p) {
+    after_previous_kernel();
+    extern __shared__ __align__(16) float raw[];   // Q row, K row, V row; then cos and sin [rotary_dim / 2]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int hd = p.head_dim;
+    const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
+    const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    const int half = p.rotary_dim / 2;
+    float* s_cos = raw + all_width;
+    float* s_sin = s_cos + half;
+    const InT* src = (const InT*)p.qkv + (size_t)t * all_width;
+    const WT* qw = (const WT*)p.q_weight;
+    const WT* kw = (const WT*)p.k_weight;
+
+    const int pos = p.tok_pos[t];
+    const int slot = p.tok_slot[t];
+    float ssq = 0.f, ssk = 0.f;
+    for (int base = 0; base < all_width; base += 4 * QKV_VEC_BATCH * NORM_BLOCK) {
+        float4 v[QKV_VEC_BATCH], w[QKV_VEC_BATCH];
+#pragma unroll
+        for (int u = 0; u < QKV_VEC_BATCH; ++u) {
+            const int i = base + 4 * (u * NORM_BLOCK + threadIdx.x);
+            v[u] = i < all_width ? load4<InT>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[u] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (i < q_width) { if (qw) w[u] = load4<WT>(qw + i); }
+            else if (i < qk_width) { if (kw) w[u] = load4<WT>(kw + i - q_width); }
+        }
+#pragma unroll
+        for (int u = 0; u < QKV_VEC_BATCH; ++u) {
+            const int i = base + 4 * (u * NORM_BLOCK + threadIdx.x);
+            if (i < all_width)
+                *reinterpret_cast<float4*>(raw + i) = make_float4(v[u].x * w[u].x, v[u].y * w[u].y, v[u].z * w[u].z, v[u].w * w[u].w);
+            const float ss = v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+            if (i < q_width) ssq += ss;
+            else if (i < qk_width) ssk += ss;
+        }
+    }
+    const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
+    for (int j = threadIdx.x; j < half; j += NORM_BLOCK) {
+        s_cos[j] = p.cos_table[(size_t)table_row * half + j];
+        s_sin[j] = p.sin_table[(size_t)table_row * half + j];
+    }
+    const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
+    const int in_page = pos % FRB_PAGE;
+    float rinv_q = 1.f, rinv_k = 1.f;
+    if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
+    if (kw) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
+    __syncthreads();
+
+    for (int i = 4 * threadIdx.x; i < qk_width; i += 4 * NORM_BLOCK) {
+        const bool is_q = i < q_width;
+        const float* base = is_q ? raw : raw + q_width;
+        const float rinv = is_q ? rinv_q : rinv_k;
+        const int local = is_q ? i : i - q_width;
+        const int head = local / hd, dim = local - head * hd;
+        float4 a = *reinterpret_cast<const float4*>(base + local);
+        a = make_float4(a.x * rinv, a.y * rinv, a.z * rinv, a.w * rinv);
+        if (dim < p.rotary_dim) {
+            // a' = a c - b s ; b' = b c + a s   (src/minimax.rs:78-81)
+            if (p.interleaved) {                 // pairs (x, y) and (z, w) of this group, angles dim/2 and dim/2 + 1
+                const int j = dim >> 1;
+                const float c0 = s_cos[j], s0 = s_sin[j], c1 = s_cos[j + 1], s1 = s_sin[j + 1];
+                a = make_float4(a.x * c0 - a.y * s0, a.y * c0 + a.x * s0, a.z * c1 - a.w * s1, a.w * c1 + a.z * s1);
+            } else {
+                const bool first = dim < half;
+                const int j = first ? dim : dim - half;
+                float4 b = *reinterpret_cast<const float4*>(base + (first ? local + half : local - half));
+                b = make_float4(b.x * rinv, b.y * rinv, b.z * rinv, b.w * rinv);
+                const float4 c = *reinterpret_cast<const float4*>(s_cos + j), sn = *reinterpret_cast<const float4*>(s_sin + j);
+                if (first) a = make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w);
+                else a = make_float4(a.x * c.x + b.x * sn.x, a.y * c.y + b.y * sn.y, a.z * c.z + b.z * sn.z, a.w * c.w + b.w * sn.w);
+            }
+        }
+        if (is_q) {
+            store4<OutT>((OutT*)p.q_out + (size_t)t * q_width + local, a);
+        } else if (page >= 0) {
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * FRB_PAGE + in_page) * hd + dim;
+            store4<OutT>((OutT*)p.k_pages + at, a);
+        }
+    }
+    if (page >= 0) {
+        const float* vrow = raw + qk_width;
+        for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
+            const int head = i / hd, dim = i - head * hd;
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
+            ((OutT*)p.v_pages)[at] = from_f32<OutT>(vrow[i]);
+        }
+    }
+}
+
 FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight, const void* k_weight, int weight_dtype,
                             float eps, const float* cos_table, const float* sin_table, int table_positions,
                             const int* tok_pos, const int* tok_slot, const int* page_table, int max_pages,
@@ -259,15 +376,20 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim) * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + 2 kv heads) * head_dim = %d needs more than 200 KB of shared memory",
                   (num_heads + 2 * num_kv_heads) * head_dim);
+    const int in_bytes = in_dtype == FRB_F32 ? 4 : 2, out_bytes = out_dtype == FRB_F32 ? 4 : 2, w_bytes = weight_dtype == FRB_F32 ? 4 : 2;
+    const auto aligned = [](const void* ptr, int bytes) { return ((uintptr_t)ptr & (size_t)(4 * bytes - 1)) == 0; };
+    const bool by_four = head_dim % 4 == 0 && rotary_dim % (interleaved ? 4 : 8) == 0 && aligned(qkv, in_bytes) &&
+                         aligned(q_out, out_bytes) && aligned(k_pages, out_bytes) && aligned(q_weight, w_bytes) &&
+                         aligned(k_weight, w_bytes);
     FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
         if (num_tokens <= NORM_FEW_ROWS) {
-            auto kernel = qkv_prepare_kernel<InT, OutT, WT, 1024>;
+            auto kernel = by_four ? qkv_prepare_vec_kernel<InT, OutT, WT, 1024> : qkv_prepare_kernel<InT, OutT, WT, 1024>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<num_tokens, 1024, smem, stream>>>(p);
+            launch_dependent(kernel, dim3(num_tokens), dim3(1024), smem, stream, p);
         } else {
-            auto kernel = qkv_prepare_kernel<InT, OutT, WT, 256>;
+            auto kernel = by_four ? qkv_prepare_vec_kernel<InT, OutT, WT, 256> : qkv_prepare_kernel<InT, OutT, WT, 256>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<num_tokens, 256, smem, stream>>>(p);
+            launch_dependent(kernel, dim3(num_tokens), dim3(256), smem, stream, p);
         }
     })));
     FRB_RETURN_LAUNCH("qkv_prepare");
@@ -277,13 +399,14 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
 
 // x[i] += delta[i]  (float32 residual sum when no norm follows)
 __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, size_t n) {
+    after_previous_kernel();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += delta[i];
 }
 
 FRB_API int frb_add_rows(float* x, const float* delta, long long n, cudaStream_t stream) {
     if (n == 0) return 0;
-    add_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, delta, (size_t)n);
+    launch_dependent(add_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, delta, (size_t)n);
     FRB_RETURN_LAUNCH("add_rows");
 }
 

@@ -40,6 +40,7 @@ expert_gemm_mma_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, c
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const int* __restrict__ num_tiles, const int* __restrict__ offsets, OutT* __restrict__ out, int F, int K,
                        int k_per_split, int groups) {
+    after_previous_kernel();
     extern __shared__ float partial[];       // [splits - 1][groups][NACC][32]
     constexpr int NACC = NB * 4 * (PAIRED ? 2 : 1);
     const int tile = blockIdx.x;
@@ -164,10 +165,10 @@ FRB_API int frb_expert_gemm_mma(const void* W, const void* X, const int* x_rows,
     const size_t smem = (size_t)(splits - 1) * groups * nb * 4 * (paired ? 2 : 1) * 32 * sizeof(float);
 #define LAUNCH(NB)                                                                                                        \
     if (paired)                                                                                                           \
-        expert_gemm_mma_kernel<NB, true, bf16><<<grid, threads, smem, stream>>>(                                          \
+        launch_dependent(expert_gemm_mma_kernel<NB, true, bf16>, dim3(grid), dim3(threads), smem, stream,                                           \
             (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (bf16*)out, F, K, k_per_split, groups); \
     else                                                                                                                  \
-        expert_gemm_mma_kernel<NB, false, float><<<grid, threads, smem, stream>>>(                                        \
+        launch_dependent(expert_gemm_mma_kernel<NB, false, float>, dim3(grid), dim3(threads), smem, stream,                                         \
             (const bf16*)W, (const bf16*)X, x_rows, tile_expert, tile_row0, num_tiles, offsets, (float*)out, F, K, k_per_split, groups)
     if (tile_rows == 8) { LAUNCH(1); } else if (tile_rows == 16) { LAUNCH(2); } else { LAUNCH(4); }
 #undef LAUNCH

@@ -121,6 +121,7 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
 __global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int num_experts,
                                    int top_k, int renormalize, float routed_scale, int* __restrict__ ids,
                                    float* __restrict__ weights) {
+    after_previous_kernel();
     extern __shared__ float sm[];
     const int t = blockIdx.x;
     pick_experts(logits + (size_t)t * num_experts, bias, num_experts, top_k, renormalize, routed_scale, sm, sm + num_experts,
@@ -133,7 +134,7 @@ FRB_API int frb_router_topk(const float* logits, const float* bias, int num_toke
     FRB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "router: top_k %d is outside 1..%d experts", top_k, num_experts);
     const size_t smem = (size_t)2 * num_experts * sizeof(float);
     FRB_CHECK_ARG(smem <= 48 * 1024, "router: %d experts exceed the kernel's 6144", num_experts);
-    router_topk_kernel<<<num_tokens, 32, smem, stream>>>(logits, bias, num_experts, top_k, renormalize, routed_scale, ids,
+    launch_dependent(router_topk_kernel, dim3(num_tokens), dim3(32), smem, stream, logits, bias, num_experts, top_k, renormalize, routed_scale, ids,
                                                          weights);
     FRB_RETURN_LAUNCH("router_topk");
 }
@@ -361,6 +362,7 @@ __device__ __forceinline__ void route_and_plan(const SmallRouteParams& p, float*
 }
 
 __global__ void __launch_bounds__(SMALL_WARPS * 32) route_plan_small_kernel(SmallRouteParams p) {
+    after_previous_kernel();
     extern __shared__ float sm[];
     __shared__ int s_ids[SMALL_MAX_ASSIGN];
     route_and_plan(p, sm, s_ids);
@@ -376,6 +378,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_plan_small_kernel(Smal
 __global__ void __launch_bounds__(SMALL_WARPS * 32)
 router_small_kernel(const float* __restrict__ act, const float* __restrict__ router, int width, float* __restrict__ logits,
                     unsigned int* __restrict__ ticket, SmallRouteParams p) {
+    after_previous_kernel();
     extern __shared__ float sm[];
     __shared__ int s_ids[SMALL_MAX_ASSIGN];
     __shared__ float s_part[SMALL_WARPS][ROUTER_SMALL_TOKENS];
@@ -459,7 +462,7 @@ FRB_API int frb_route_plan_small(const float* logits, const float* bias, int num
         return -1;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(route_plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    route_plan_small_kernel<<<1, SMALL_WARPS * 32, smem, stream>>>(p);
+    launch_dependent(route_plan_small_kernel, dim3(1), dim3(SMALL_WARPS * 32), smem, stream, p);
     FRB_RETURN_LAUNCH("route_plan_small");
 }
 
@@ -481,7 +484,7 @@ FRB_API int frb_router_small(const float* act, const float* router, int width, f
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int blocks = (num_experts + ROUTER_SMALL_EXPERTS - 1) / ROUTER_SMALL_EXPERTS;
-    router_small_kernel<<<blocks, SMALL_WARPS * 32, smem, stream>>>(act, router, width, logits, ticket, p);
+    launch_dependent(router_small_kernel, dim3(blocks), dim3(SMALL_WARPS * 32), smem, stream, act, router, width, logits, ticket, p);
     FRB_RETURN_LAUNCH("router_small");
 }
 
@@ -490,6 +493,7 @@ FRB_API int frb_router_small(const float* act, const float* router, int width, f
 // out[t, :] = sum_{r < k} w[t, r] * y[row_of_assign[t*k + r], :], added in rank order.
 __global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
                                const int* __restrict__ row_of_assign, int top_k, int width, float* __restrict__ out) {
+    after_previous_kernel();
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= width) return;
@@ -506,6 +510,6 @@ FRB_API int frb_expert_combine(const float* y, const float* weights, const int* 
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens, (width + 255) / 256);
     FRB_CHECK_ARG(grid.y <= 65535, "combine: a width of %d exceeds the grid", width);
-    combine_kernel<<<grid, 256, 0, stream>>>(y, weights, row_of_assign, top_k, width, out);
+    launch_dependent(combine_kernel, dim3(grid), dim3(256), 0, stream, y, weights, row_of_assign, top_k, width, out);
     FRB_RETURN_LAUNCH("expert_combine");
 }

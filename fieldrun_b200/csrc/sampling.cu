@@ -16,6 +16,7 @@ __device__ __forceinline__ void keep_larger(float& best, int& best_i, float v, i
 __global__ void __launch_bounds__(SAMPLE_BLOCK)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const float* __restrict__ uniform, int* __restrict__ out) {
+    after_previous_kernel();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ float s_sum[32];
@@ -100,6 +101,6 @@ FRB_API int frb_sample_rows(const float* logits, int rows, int vocab, const floa
     if (rows == 0) return 0;
     FRB_CHECK_ARG(vocab >= 1, "sampling: a vocabulary of %d", vocab);
     FRB_CHECK_ARG(temperature == nullptr || uniform != nullptr, "sampling: temperatures without uniform numbers");
-    sample_rows_kernel<<<rows, SAMPLE_BLOCK, 0, stream>>>(logits, vocab, temperature, uniform, out);
+    launch_dependent(sample_rows_kernel, dim3(rows), dim3(SAMPLE_BLOCK), 0, stream, logits, vocab, temperature, uniform, out);
     FRB_RETURN_LAUNCH("sample_rows");
 }

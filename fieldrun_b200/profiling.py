@@ -7,7 +7,8 @@ Each case holds between a few hundred MB and 2 GB on the device (more than the L
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
 arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
 ``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``
-(mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries).
+(mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries),
+``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
 this library's own.
 """
@@ -142,44 +143,59 @@ def attention(kind: str, launches: int) -> dict:
     return {"case": f"attention_{kind}", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
 
 
-def small_kernels(launches: int) -> dict:
-    """The latency-bound kernels of a decode step of 8 sequences, each launched back to back."""
+def small_kernels(launches: int, tokens: int) -> dict:
+    """The kernels around the matrix products of a step of `tokens` tokens (8: a decode step of 8 sequences;
+    2048: a prompt), each launched back to back from one CUDA graph.  Microseconds per launch."""
     dev = torch.device("cuda")
-    launches = max(launches, 200)            # a replay's own cost, spread over few launches, would show in each
-    tokens, experts_n, top_k = 8, 256, 8
-    out = {"case": "decode_small_kernels", "tokens": tokens}
+    launches = max(launches, 200 if tokens <= 64 else 20)   # a replay's own cost, spread over few launches, would show
+    experts_n, top_k = 256, 8
+    out = {"case": "decode_small_kernels" if tokens <= 64 else "prefill_small_kernels", "tokens": tokens}
+    us = lambda launch: round(1000 * _time_recorded(launch, launches), 2)
     x = torch.randn(tokens, HIDDEN, device=dev)
     delta = torch.randn(tokens, HIDDEN, device=dev)
     weight = torch.ones(HIDDEN, device=dev)
     act = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev)
     act32 = torch.empty(tokens, HIDDEN, device=dev)
-    out["rmsnorm_us"] = round(1000 * _time_recorded(lambda: ops.rmsnorm(x, weight, 1e-6, act, delta=delta, out32=act32, write_back=True), launches), 2)
+    out["rmsnorm_us"] = us(lambda: ops.rmsnorm(x, weight, 1e-6, act, delta=delta, out32=act32, write_back=True))
     router = torch.randn(experts_n, HIDDEN, device=dev) * 0.02
     bias = torch.zeros(experts_n, device=dev)
     n = tokens * top_k
     i32 = lambda k: torch.zeros(k, dtype=torch.int32, device=dev)
     ids, weights = torch.zeros(tokens, top_k, dtype=torch.int32, device=dev), torch.zeros(tokens, top_k, device=dev)
     lists = [i32(experts_n + 1), i32(n), i32(n), i32(n + experts_n), i32(n + experts_n), i32(1)]
-    logits = torch.empty(tokens, experts_n, device=dev)
-    out["router_small_us"] = round(1000 * _time_recorded(lambda: ops.router_small(act32, router, logits, bias, top_k, True, 1.0, 8, ids, weights, *lists), launches), 2)
-    out["route_plan_small_us"] = round(1000 * _time_recorded(lambda: ops.route_plan_small(logits, bias, top_k, True, 1.0, 8, ids, weights, *lists), launches), 2)
+    logits = torch.randn(tokens, experts_n, device=dev)
+    if tokens <= ops.ROUTER_SMALL_TOKENS:
+        scratch = torch.empty(tokens, experts_n, device=dev)
+        out["router_small_us"] = us(lambda: ops.router_small(act32, router, scratch, bias, top_k, True, 1.0, 8, ids, weights, *lists))
+    if tokens <= ops.SMALL_ROUTE_TOKENS:
+        out["route_plan_small_us"] = us(lambda: ops.route_plan_small(logits, bias, top_k, True, 1.0, 8, ids, weights, *lists))
+    out["router_topk_us"] = us(lambda: ops.router_topk(logits, bias, top_k, True, 1.0, ids, weights))
+    counts = i32(((n + 1023) // 1024) * experts_n)
+    out["expert_plan_us"] = us(lambda: ops.expert_plan(ids, experts_n, 8, counts, *lists))
     qkv = torch.randn(tokens, (HEADS + 2 * KV_HEADS) * HEAD_DIM, device=dev)
     qw, kw = torch.ones(HEADS * HEAD_DIM, device=dev), torch.ones(KV_HEADS * HEAD_DIM, device=dev)
-    cos, sin = torch.ones(4096, 32, device=dev), torch.zeros(4096, 32, device=dev)
-    pos = torch.full((tokens,), 3000, dtype=torch.int32, device=dev)
-    slots = torch.arange(tokens, dtype=torch.int32, device=dev)
-    pages = tokens * 64
+    positions = 4096
+    cos, sin = torch.ones(positions, 32, device=dev), torch.zeros(positions, 32, device=dev)
+    if tokens <= 64:         # one token each of `tokens` sequences, deep in their contexts
+        pos = torch.full((tokens,), 3000, dtype=torch.int32, device=dev)
+        slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+        pages = tokens * 64
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(tokens, 64).contiguous()
+    else:                    # one prompt
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+        slots = torch.zeros(tokens, dtype=torch.int32, device=dev)
+        pages = (tokens + 63) // 64
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages).contiguous()
     keys = torch.zeros(pages, KV_HEADS, 64, HEAD_DIM, dtype=torch.bfloat16, device=dev)
     values = torch.zeros(pages, KV_HEADS, HEAD_DIM, 64, dtype=torch.bfloat16, device=dev)
-    table = torch.arange(pages, dtype=torch.int32, device=dev).view(tokens, 64).contiguous()
     q = torch.empty(tokens, HEADS * HEAD_DIM, dtype=torch.bfloat16, device=dev)
-    out["qkv_prepare_us"] = round(1000 * _time_recorded(lambda: ops.qkv_prepare(qkv, qw, kw, 1e-6, cos, sin, pos, slots, table, q, keys, values,
-                                                                       num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, rotary_dim=64,
-                                                                       interleaved=False, write_cache=True), launches), 2)
+    out["qkv_prepare_us"] = us(lambda: ops.qkv_prepare(qkv, qw, kw, 1e-6, cos, sin, pos, slots, table, q, keys, values,
+                                                       num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, rotary_dim=64,
+                                                       interleaved=False, write_cache=True))
     y = torch.randn(n, HIDDEN, device=dev)
     rowmap = torch.arange(n, dtype=torch.int32, device=dev)
-    out["rmsnorm_with_experts_us"] = round(1000 * _time_recorded(lambda: ops.rmsnorm(x, weight, 1e-6, act, out32=act32, write_back=True,
-                                                                            experts=(y, weights.abs() + 0.1, rowmap)), launches), 2)
+    out["rmsnorm_with_experts_us"] = us(lambda: ops.rmsnorm(x, weight, 1e-6, act, out32=act32, write_back=True,
+                                                            experts=(y, weights.abs() + 0.1, rowmap)))
     return out
 
 
@@ -189,7 +205,8 @@ CASES = {
     "attention_decode": lambda n: attention("decode", n),
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
-    "decode_small_kernels": small_kernels,
+    "decode_small_kernels": lambda n: small_kernels(n, 8),
+    "prefill_small_kernels": lambda n: small_kernels(n, 2048),
 }
 
 

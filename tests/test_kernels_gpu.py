@@ -90,19 +90,22 @@ def paged_cache(rng, slots, pages, kv_heads, head_dim, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,normed,interleaved", [
     (6, 2, 32, 16, True, False), (5, 5, 24, 24, False, False), (8, 1, 128, 64, True, False),
-    (4, 2, 16, 8, True, True), (3, 3, 20, 0, True, False)])
-def test_qk_norm_rotary_and_cache_write(dtype, heads, kv_heads, head_dim, rotary, normed, interleaved):
+    (4, 2, 16, 8, True, True), (3, 3, 20, 0, True, False),
+    # sizes that the four-wide kernel does not take: a head size, a half-split and an interleaved rotation width
+    (3, 1, 18, 6, True, False), (2, 2, 12, 4, True, False), (4, 2, 16, 6, True, True)])
+@pytest.mark.parametrize("many", [False, True], ids=["few", "many"])
+def test_qk_norm_rotary_and_cache_write(dtype, heads, kv_heads, head_dim, rotary, normed, interleaved, many):
     from fieldrun_b200.parts.position import Rotary
     rng = np.random.default_rng(2)
-    T = 11
+    T = 11 + (64 if many else 0)         # more than 64 tokens run in smaller blocks
     qw, kw = heads * head_dim, kv_heads * head_dim
     qkv = rng.normal(size=(T, qw + 2 * kw)).astype(np.float32)
     wq = (1 + 0.2 * rng.normal(size=qw)).astype(np.float32)
     wk = (1 + 0.2 * rng.normal(size=kw)).astype(np.float32)
-    positions = np.array([0, 1, 2, 63, 64, 65, 130, 5, 6, 7, 191], dtype=np.int32)
-    slot_of = np.array([0, 0, 0, 0, 0, 0, 0, 2, 2, 2, 2], dtype=np.int32)
+    positions = np.array([0, 1, 2, 63, 64, 65, 130, 5, 6, 7, 191] + (list(range(64)) if many else []), dtype=np.int32)
+    slot_of = np.array([0, 0, 0, 0, 0, 0, 0, 2, 2, 2, 2] + ([1] * 64 if many else []), dtype=np.int32)
     keys, values, table, free = paged_cache(rng, 3, 12, kv_heads, head_dim, dtype)
-    for slot, need in ((0, 3), (2, 3)):
+    for slot, need in ((0, 3), (2, 3), (1, 1)):
         for i in range(need):
             table[slot, i] = free.pop()
     cos = sin = None
