@@ -368,16 +368,18 @@ def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: 
           _ptr(tile_row0), _ptr(num_tiles))
 
 
-def stream_shape(tiles: int, features: int, inner: int, tile_rows: int) -> dict:
-    """How a block of the streaming kernel is cut: with many tiles 4 groups of 16 features and the whole
-    inner size; with few tiles fewer groups per block (more blocks, about two per SM or more) and the inner
-    size in parts (about 2048 warps streaming).  Returns the keyword arguments ``splits`` and ``groups``."""
+def stream_shape(tiles: int, features: int, inner: int, tile_rows: int, paired: bool = False) -> dict:
+    """How a block of the streaming kernel is cut.  Measured on a B200 at MiniMax-M2's sizes: one group of 16
+    features per block with the inner size cut into parts among the block's warps is never slower than
+    several groups over the whole inner size, and it is faster where few tiles leave the device short of
+    bytes in flight: about 4096 warps for a plain product (a warp keeps 4 KB in flight), about 1536 for a
+    paired one (8 KB), and at least two parts.  Returns the keyword arguments ``splits`` and ``groups``."""
     nb = tile_rows // 8
     total = max(1, tiles * ((features + 15) // 16))
-    groups = 4 if total >= 4 * 296 else 2 if total >= 2 * 296 else 1
-    most = max(1, 16 // (nb * groups))
-    splits = max(1, min(most, -(-2048 // total), max(1, inner // 256)))
-    return {"splits": splits, "groups": groups}
+    most = max(1, 16 // nb)
+    want = -(-(1536 if paired else 4096) // total)
+    splits = max(1, min(most, max(2, want), max(1, inner // 128)))
+    return {"splits": splits, "groups": 1}
 
 
 _TC_STATUS: dict[str, torch.Tensor] = {}

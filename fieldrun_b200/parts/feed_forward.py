@@ -156,7 +156,7 @@ class RoutedExperts(FeedForward):
             tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
             ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],
                                 p["offsets"], p["max_tiles"], p["tile_rows"], hidden, paired=True,
-                                **ops.stream_shape(tiles, self.expert_width, self.hidden_size, p["tile_rows"]))
+                                **ops.stream_shape(tiles, self.expert_width, self.hidden_size, p["tile_rows"], paired=True))
             ops.expert_gemm_mma(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                 p["max_tiles"], p["tile_rows"], y, paired=False,
                                 **ops.stream_shape(tiles, self.hidden_size, self.expert_width, p["tile_rows"]))

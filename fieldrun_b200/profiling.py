@@ -83,7 +83,7 @@ def experts(kind: str, launches: int) -> dict:
             ops.expert_gemm_tc(w2, hidden, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False)
         else:
             ops.expert_gemm_mma(w13, x, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True,
-                                **ops.stream_shape(tiles, WIDTH, HIDDEN, tile_rows))
+                                **ops.stream_shape(tiles, WIDTH, HIDDEN, tile_rows, paired=True))
             ops.expert_gemm_mma(w2, hidden, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False,
                                 **ops.stream_shape(tiles, HIDDEN, WIDTH, tile_rows))
 

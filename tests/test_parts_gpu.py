@@ -433,6 +433,109 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
     engine.cache.check()
 
 
+def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_are_registered_built_and_stepped():
+    """Two more parts defined here and plugged in by name: a position encoding whose angles grow linearly
+    with the pair's index (not geometrically), and a feed-forward that sends each row to one of two maps by
+    the sign of a learned projection.  Neither is anyone's model; they show that the interfaces carry them."""
+    _, config, engine_mod, parts, weights_mod = lib()
+
+    class LinearAngles(parts.Position):
+        def __init__(self, args):
+            self.rotary_dim = int(args["rotary_dim"])
+            self.step = float(args["step"])
+            self.interleaved = False
+
+        def tables(self, num_positions, device):
+            j = torch.arange(1, self.rotary_dim // 2 + 1, dtype=torch.float64)
+            angles = torch.arange(num_positions, dtype=torch.float64)[:, None] * (self.step * j)[None, :]
+            return angles.cos().float().to(device), angles.sin().float().to(device)
+
+    class SignRouted(parts.FeedForward):
+        wants_float32_input = True
+
+        def __init__(self, spec, dtype):
+            super().__init__(spec, dtype)
+            self.width = int(spec.args["width"])
+
+        def tensor_needs(self):
+            m = weights_mod.TensorNeed
+            return [m(self.name_of("gate"), (self.width,), weights_mod.VECTOR, "normal"),
+                    m(self.name_of("left"), (self.width, self.width), weights_mod.MATRIX, "normal"),
+                    m(self.name_of("right"), (self.width, self.width), weights_mod.MATRIX, "normal")]
+
+        def load(self, src):
+            self.gate, self.left, self.right = (src.fetch(n) for n in self.tensor_needs())
+
+        def forward(self, ctx, act, act32):
+            goes_left = (act32 @ self.gate) > 0
+            both = torch.stack([act.float() @ self.right.float().T, act.float() @ self.left.float().T])
+            return torch.where(goes_left[:, None], both[1], both[0]).contiguous()
+
+    parts.register_part("position", "linear_angles", LinearAngles, replace=True)
+    parts.register_part("feed_forward", "sign_routed", SignRouted, replace=True)
+    norm = lambda name: config.PartSpec("rmsnorm", {"width": HIDDEN, "eps": 1e-5}, {"weight": name})
+    attention = attention_spec(config, HIDDEN, 4, 2, 16, 8, False, prefix="B.")
+    attention.args["position"] = {"kind": "linear_angles", "rotary_dim": 8, "step": 0.37}
+    layer = config.LayerSpec("pre_norm", attention,
+                             config.PartSpec("sign_routed", {"width": HIDDEN}, {"gate": "r.gate", "left": "r.left", "right": "r.right"}),
+                             norm("n1"), norm("n2"))
+    plan = config.ModelPlan("toy-routed", HIDDEN, VOCAB,
+                            config.PartSpec("token_embedding", {"vocab_size": VOCAB, "width": HIDDEN}, {"weight": "emb"}),
+                            (layer,), (config.RunSpec(0, 0),), norm("fn"),
+                            config.PartSpec("vocab_head", {"vocab_size": VOCAB, "width": HIDDEN}, {"weight": "head"}))
+    rng = np.random.default_rng(6)
+    W = {"emb": rng.normal(size=(VOCAB, HIDDEN)), "head": rng.normal(size=(VOCAB, HIDDEN)) * 0.2,
+         "r.gate": rng.normal(size=HIDDEN), "r.left": rng.normal(size=(HIDDEN, HIDDEN)) * 0.1,
+         "r.right": rng.normal(size=(HIDDEN, HIDDEN)) * 0.1}
+    for n in ("n1", "n2", "fn"):
+        W[n] = 1 + 0.1 * rng.normal(size=HIDDEN)
+    W.update(attention_weights(rng, HIDDEN, 4, 2, 16, False, "B."))
+    W = {k: np.asarray(v, dtype=np.float32).astype(np.float64) for k, v in W.items()}
+    model = engine_mod.DecoderModel(plan, "float32")
+    model.load(source(W, "float32"))
+    engine = engine_mod.Engine(model, max_tokens=512, num_slots=2)
+
+    def turn(x, heads, pos):
+        out = x.copy()
+        ang = pos[:, None] * (0.37 * np.arange(1, 5))[None, :]
+        for h in range(heads):
+            a, b = x[:, h * 16:h * 16 + 4], x[:, h * 16 + 4:h * 16 + 8]
+            out[:, h * 16:h * 16 + 4] = a * np.cos(ang) - b * np.sin(ang)
+            out[:, h * 16 + 4:h * 16 + 8] = b * np.cos(ang) + a * np.sin(ang)
+        return out
+
+    def plain(ids):
+        x = W["emb"][ids]
+        a = pm.rms_norm(x, W["n1"], 1e-5)
+        pos = np.arange(len(ids), dtype=np.float64)
+        q, k, v = (a @ W[f"B.self_attn.{n}_proj.weight"].T for n in "qkv")
+        x = x + pm.causal_attention(turn(q, 4, pos), turn(k, 2, pos), v, 4, 2, 16, 0.25) @ W["B.self_attn.o_proj.weight"].T
+        a = pm.rms_norm(x, W["n2"], 1e-5)
+        side = a @ W["r.gate"]
+        x = x + np.where((side > 0)[:, None], a @ W["r.left"].T, a @ W["r.right"].T)
+        return pm.rms_norm(x, W["fn"], 1e-5) @ W["head"].T, np.abs(side)
+
+    requests = [rng.integers(0, VOCAB, size=n) for n in (70, 33)]
+    slots = [engine.new_sequence() for _ in requests]
+    heads = [50, 20]
+    out = f64(engine.step(slots, [r[:h].tolist() for r, h in zip(requests, heads)], [list(range(h)) for h in heads]))
+    rows = [[out[:50]], [out[50:]]]
+    for step in range(20):
+        live = [b for b in range(2) if heads[b] + step < len(requests[b])]
+        out = f64(engine.step([slots[b] for b in live], [[int(requests[b][heads[b] + step])] for b in live]))
+        for row, b in enumerate(live):
+            rows[b].append(out[row:row + 1])
+    for s in slots:
+        engine.release(s)
+    engine.cache.check()
+    for r, got in zip(requests, rows):
+        ref, margin = plain(r)
+        sure = margin > 1e-4                  # a row whose side is decided by rounding may go either way
+        assert sure.sum() >= len(r) - 2
+        # a wrong side at one position changes only that position's own row here (one layer)
+        close(np.concatenate(got)[sure], ref[sure], 1e-5, f"toy position and toy routing, request of {len(r)}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embedding_and_head_parts(dtype):
     _, config, _, parts, _ = lib()
