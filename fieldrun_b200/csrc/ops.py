@@ -33,6 +33,7 @@ _SIGNATURES = {
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifii",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
+    "frb_attention_decode_tma": "pppipipppppiiiifiip",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
@@ -101,7 +102,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_expert_plan": 3, "frb_attention_decode_mma": 2}
+_KERNELS_PER_CALL = {"frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
 
 
 def launches() -> int:
@@ -326,6 +327,20 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           head_dim, float(scale), int(window or 0), max_chunks)
 
 
+def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                         seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                         out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                         window: Optional[int], max_chunks: int) -> None:
+    """As :func:`attention_decode_mma` for head sizes 64 and 128, with the pages copied into shared memory by
+    TMA (all pages of a block at once), which keeps far more bytes in flight."""
+    for t in (q, k_pages, v_pages, out):
+        _want(t, torch.bfloat16, "tensor-core attention operands")
+    _want(part_o, torch.float32, "partial outputs")
+    _call("frb_attention_decode_tma", _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
+          page_table.shape[1], _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads,
+          num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)))
+
+
 def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                           tile_seq: torch.Tensor, tile_q0: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
                           seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
@@ -402,8 +417,9 @@ def tc_status_check(device) -> None:
         if code != 0:
             _TC_STATUS[key].zero_()
             where = {1: "the producer waiting for a free stage", 2: "the MMA thread waiting for a loaded stage",
-                     3: "the epilogue waiting for the accumulators"}.get(code, f"code {code}")
-            raise KernelError(f"expert_gemm_tc: a wait gave up ({where}); the step's results are not valid")
+                     3: "the epilogue waiting for the accumulators",
+                     4: "one-token attention waiting for a page's copy"}.get(code, f"code {code}")
+            raise KernelError(f"a tensor-core kernel's wait gave up ({where}); the step's results are not valid")
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

@@ -116,8 +116,10 @@ class GQAAttention(Mixer):
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
                 part_ml = ctx.buffer("attention.part_ml", (ctx.num_seqs, self.num_heads, chunks, 2), torch.float32)
-                ops.attention_decode_mma(q, line.keys, line.values, line.page_table, ctx.seq_start, ctx.seq_slot, part_o,
-                                         part_ml, out, max_chunks=chunks, **common)
+                # head sizes 64 and 128: the pages come into shared memory by TMA; others: loads into registers
+                decode = ops.attention_decode_tma if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS else ops.attention_decode_mma
+                decode(q, line.keys, line.values, line.page_table, ctx.seq_start, ctx.seq_slot, part_o, part_ml, out,
+                       max_chunks=chunks, **common)
             elif self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and ctx.max_q_len >= TC_ATTENTION_MIN_QUERIES:
                 # prompts: 128 queries of one head per block, both products on tcgen05
                 tile_seq, tile_q0 = ctx.query_tiles(ops.TC_ATTENTION_QUERIES)

@@ -6,7 +6,8 @@ profilers.
 Each case holds between a few hundred MB and 2 GB on the device (more than the L2 cache, far less than a model), runs a few
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
 arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
-``experts_stream`` (decode-sized expert products, streamed), ``attention_decode``, ``attention_prefill``
+``experts_stream`` (decode-sized expert products, streamed), ``attention_decode`` (pages by TMA),
+``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
 (mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries),
 ``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
@@ -98,7 +99,7 @@ def experts(kind: str, launches: int) -> dict:
 
 def attention(kind: str, launches: int) -> dict:
     dev = torch.device("cuda")
-    batch, context = (8, 4096) if kind == "decode" else (1, 2048)
+    batch, context = (32, 4096) if kind.startswith("decode") else (1, 2048)
     pages_per = context // 64
     pages = batch * pages_per
     keys = (torch.randn(pages, KV_HEADS, 64, HEAD_DIM, device=dev) * 0.3).to(torch.bfloat16)
@@ -106,19 +107,20 @@ def attention(kind: str, launches: int) -> dict:
     table = torch.arange(pages, dtype=torch.int32, device=dev).view(batch, pages_per).contiguous()
     slots = torch.arange(batch, dtype=torch.int32, device=dev)
     scale = HEAD_DIM ** -0.5
-    if kind == "decode":
+    if kind.startswith("decode"):
         q = torch.randn(batch, HEADS * HEAD_DIM, device=dev).to(torch.bfloat16)
         out = torch.empty_like(q)
         positions = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
         chunks = context // ops.ATTENTION_CHUNK
         part_o = torch.empty(batch, HEADS, chunks, HEAD_DIM, dtype=torch.float32, device=dev)
         part_ml = torch.empty(batch, HEADS, chunks, 2, dtype=torch.float32, device=dev)
-        launch = lambda: ops.attention_decode_mma(q, keys, values, table, positions, slots, part_o, part_ml, out, num_heads=HEADS,
-                                                  num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None,
-                                                  max_chunks=chunks)
+        decode = ops.attention_decode_tma if kind == "decode" else ops.attention_decode_mma
+        launch = lambda: decode(q, keys, values, table, positions, slots, part_o, part_ml, out, num_heads=HEADS,
+                                num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None, max_chunks=chunks)
         ms = _time(launch, launches)
+        ops.tc_status_check(dev)
         kv_bytes = (keys.numel() + values.numel()) * 2
-        return {"case": "attention_decode", "ms": round(ms, 4), "batch": batch, "context": context,
+        return {"case": "attention_" + kind, "ms": round(ms, 4), "batch": batch, "context": context,
                 "kv_gb_per_s": round(kv_bytes / ms / 1e6, 1)}
     q = torch.randn(context, HEADS * HEAD_DIM, device=dev).to(torch.bfloat16)
     out = torch.empty_like(q)
@@ -203,6 +205,7 @@ CASES = {
     "experts_tc": lambda n: experts("tc", n),
     "experts_stream": lambda n: experts("stream", n),
     "attention_decode": lambda n: attention("decode", n),
+    "attention_decode_mma": lambda n: attention("decode_mma", n),
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
     "decode_small_kernels": lambda n: small_kernels(n, 8),

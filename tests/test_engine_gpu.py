@@ -248,3 +248,30 @@ def test_a_layer_of_minimax_m2_size():
             assert_close(logits[key], ref, "bfloat16", f"MiniMax-M2-sized layer, request {key}")
             differs = (np.sort(own, axis=-1) != np.sort(routes, axis=-1)).any(axis=-1)
             assert not (differs & (margins > 5e-3)).any()
+
+
+def test_a_step_whose_buffers_pass_two_to_the_31_elements():
+    """A prompt of 95,000 tokens beside a short one, one layer of MiniMax-M2's own sizes: the expert outputs of
+    the step are 760,000 rows of 3,072 float32, more elements than 32-bit indices reach, and the short
+    request's rows lie at the far end of every buffer.  Its logits must be what it gets alone (no plain
+    model at this size: an index that wrapped would read or write some other row)."""
+    import fieldrun_b200 as fr
+    lm = fr.random_model(M2_SHAPED, fr.RandomInit(seed=4, matrix_std=0.02, norm_std=0.1, bias_std=0.01), dtype="bfloat16",
+                         max_tokens=96 * 1024, num_slots=2)
+    engine = lm.engine
+    rng = np.random.default_rng(12)
+    long_ids = rng.integers(0, 2003, size=95_000).tolist()
+    short_ids = rng.integers(0, 2003, size=200).tolist()
+    slot = engine.new_sequence()
+    alone = engine.step([slot], [short_ids], [[0, 100, 199]]).float().cpu().numpy()
+    engine.release(slot)
+    slots = [engine.new_sequence(), engine.new_sequence()]
+    both = engine.step(slots, [long_ids, short_ids], [[94_999], [0, 100, 199]]).float().cpu().numpy()
+    assert np.isfinite(both).all()
+    err = np.abs(both[1:] - alone).max() / np.abs(alone).max()
+    assert err <= TOLERANCE["bfloat16"], f"the short request beside a long one: relative difference {err:.3e}"
+    after = engine.step(slots, [[5], [7]]).float().cpu().numpy()          # one more token each, over the long cache
+    assert np.isfinite(after).all()
+    for s_ in slots:
+        engine.release(s_)
+    engine.cache.check()

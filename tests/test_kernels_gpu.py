@@ -357,7 +357,10 @@ def test_picking_tokens(vocab):
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 1, 128, None), (8, 8, 64, None), (32, 2, 32, None),
                                                             (12, 2, 96, 300), (48, 8, 128, 70)])
-def test_one_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window):
+@pytest.mark.parametrize("kernel", ["attention_decode_mma", "attention_decode_tma"])
+def test_one_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window, kernel):
+    if kernel == "attention_decode_tma" and head_dim not in (64, 128):
+        pytest.skip("the TMA kernel takes head sizes 64 and 128")
     rng = np.random.default_rng(11)
     lengths = {0: 1000, 1: 257, 2: 64, 4: 1, 5: 513}
     keys, values, table, free = paged_cache(rng, 6, 32, kv_heads, head_dim, "bfloat16")
@@ -374,9 +377,10 @@ def test_one_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window):
     part_o = torch.full((len(positions), heads, chunks, head_dim), float("nan"), dtype=torch.float32, device=DEV)
     part_ml = torch.full((len(positions), heads, chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
     scale = head_dim ** -0.5
-    ops().attention_decode_mma(q, keys, values, dev(table), dev(positions), dev(slot_of), part_o, part_ml, out,
-                               num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
-                               max_chunks=chunks)
+    getattr(ops(), kernel)(q, keys, values, dev(table), dev(positions), dev(slot_of), part_o, part_ml, out,
+                           num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
+                           max_chunks=chunks)
+    ops().tc_status_check(q.device)
     ref = reference_attention(f64(q), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
     close(f64(out), ref, 1e-2, "one-token attention")
     general = torch.empty_like(q)
@@ -414,7 +418,9 @@ def test_many_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window)
     close(f64(out), ref, 1e-2, "many-token attention")
 
 
-def test_tensor_core_attention_finds_one_far_key():
+@pytest.mark.parametrize("kernel", ["attention_decode_mma", "attention_decode_tma"])
+def test_tensor_core_attention_finds_one_far_key(kernel):
+    decode = getattr(ops(), kernel)
     rng = np.random.default_rng(13)
     heads, kv_heads, head_dim, n = 12, 2, 128, 900
     pages = (n + 63) // 64
@@ -432,13 +438,13 @@ def test_tensor_core_attention_finds_one_far_key():
     part_ml = torch.empty(1, heads, chunks, 2, dtype=torch.float32, device=DEV)
     out = torch.empty_like(q)
     args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=1.0)
-    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=None,
+    decode(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=None,
                                max_chunks=chunks, **args)
     close(f64(out), want, 1e-2, "far key, one token")
-    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far,
+    decode(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far,
                                max_chunks=chunks, **args)
     close(f64(out), want, 1e-2, "far key at the window's edge")
-    ops().attention_decode_mma(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far - 1,
+    decode(q, keys, values, dev(table), positions, slot_of, part_o, part_ml, out, window=n - far - 1,
                                max_chunks=chunks, **args)
     mean = np.stack([f64(values)[table[0, j // 64], :, :, j % 64] for j in range(far + 1, n)]).mean(0)
     close(f64(out), np.repeat(mean, heads // kv_heads, axis=0).reshape(1, -1), 2e-2, "one key past the window's edge")
