@@ -1,14 +1,14 @@
 // Many-token attention on the fifth-generation tensor cores (tcgen05), for prompts in bfloat16.
 //
 // The formula is the reference's (src/minimax.rs:270-281): s = q.k * scale over the keys a query may see,
-// p = softmax(s), out = p V.  A block takes 128 queries of one head.  For every cache page of 64 keys:
-//   S = Q K^T      tcgen05.mma 128 x 64 x HD, Q and the page's keys in shared memory (TMA, 128-byte swizzle),
-//                  S in tensor memory, two buffers so that the next page's product runs during this page's softmax;
+// p = softmax(s), out = p V.  A block takes 128 queries of one head.  For every step of two cache pages (128 keys):
+//   S = Q K^T      tcgen05.mma 128 x 128 x HD, Q and the pages' keys in shared memory (TMA, 128-byte swizzle),
+//                  S in tensor memory, two buffers so that the next step's product runs during this step's softmax;
 //   softmax        four warps, one thread per query row: S comes back with tcgen05.ld, running maximum and sum
 //                  in float32 registers; P (bfloat16) goes back into tensor memory with tcgen05.st;
-//   O += P V       tcgen05.mma 128 x HD x 64 with P as the tensor-memory operand and the page's transposed
+//   O += P V       tcgen05.mma 128 x HD x 64 per page with P as the tensor-memory operand and the page's transposed
 //                  values [HD][64 keys] as the shared-memory operand; O stays in tensor memory.
-// The running maximum of a row is only raised when the page's maximum exceeds it by more than 8 (in units of
+// The running maximum of a row is only raised when the step's maximum exceeds it by more than 8 (in units of
 // log2): the weights are then at most 2^8, the result is the same after the division by the row's sum, and
 // O has to be rescaled (read, multiplied, written back) only on those rare pages.
 //
@@ -21,6 +21,8 @@
 #define AT_QUERIES 128
 #define AT_THREADS 192         // warp 0: TMA producer, warp 1: MMA issuer and tensor-memory owner, warps 2-5: softmax
 #define AT_STAGES 3
+#define AT_STEP_PAGES 2        // cache pages per step of the inner loop
+#define AT_STEP_KEYS (AT_STEP_PAGES * FRB_PAGE)
 #define AT_WAIT_CYCLES (2000000000ll)
 #define AT_RAISE 8.0f          // the running maximum follows a page's maximum only beyond this margin
 
@@ -103,6 +105,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+// 2^x by the special-function unit (relative error about 2^-22; -inf and anything below -126 give 0)
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -136,8 +145,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     volatile int* failed = &failed_flag;
     constexpr int KBLOCKS = HD / 64;                           // 64 dims = one 128-byte swizzled row
     constexpr uint32_t Q_BYTES = AT_QUERIES * HD * 2, K_BYTES = FRB_PAGE * HD * 2, V_BYTES = HD * FRB_PAGE * 2;
-    constexpr uint32_t S_COL0 = 0, O_COL = 128, P_COL0 = O_COL + HD;       // S: 2 x 64 columns, O: HD, P: 2 x 32
-    constexpr uint32_t TMEM_COLS = (P_COL0 + 64) <= 256 ? 256 : 512;
+    constexpr uint32_t STAGE_BYTES = AT_STEP_PAGES * (K_BYTES + V_BYTES);
+    constexpr uint32_t K_BLOCK_BYTES = AT_STEP_KEYS * 128;     // one 64-dim block of a step's keys: [128 keys][128 bytes]
+    // tensor memory: S twice (128 columns each), O (HD columns), P twice (two bfloat16 per column: 64 columns each)
+    constexpr uint32_t S_COL0 = 0, O_COL = 2 * AT_STEP_KEYS, P_COL0 = O_COL + 128;
+    constexpr uint32_t TMEM_COLS = 512;
+    static_assert(P_COL0 + AT_STEP_KEYS <= TMEM_COLS && HD <= 128, "tensor memory layout");
 
     const int tile = blockIdx.x, head = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -148,10 +161,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int last_key = start + min(q0 + AT_QUERIES - 1, q_len - 1);
     const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
     const int first_page = first_key / FRB_PAGE, num_pages = last_key / FRB_PAGE - first_page + 1;
+    const int num_steps = (num_pages + AT_STEP_PAGES - 1) / AT_STEP_PAGES;     // a step: two pages, the last one maybe one
 
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = base;                                    // KBLOCKS tiles [128 x 64]
-    uint8_t* stage0 = base + Q_BYTES;                          // per stage: K (KBLOCKS tiles [64 x 64]) then V^T ([HD x 64])
+    uint8_t* stage0 = base + Q_BYTES;                          // per stage: K (KBLOCKS tiles [128 keys x 64]) then V^T ([HD x 64] per page)
 
     if (threadIdx.x == 0) {
         bar_init(&q_full, 1);
@@ -175,55 +189,66 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int kb = 0; kb < KBLOCKS; ++kb)
                 tma_2d(q_tile + kb * (AT_QUERIES * 128), &map_q, head * HD + kb * 64, tok0, &q_full);
-            for (int i = 0; i < num_pages; ++i) {
-                const int s = i % AT_STAGES;
-                if (!bar_wait(&kv_empty[s], ((i / AT_STAGES) & 1) ^ 1, failed)) { atomicExch(p.status, 11); break; }
-                const int page = table[first_page + i];
-                uint8_t* dst = stage0 + (size_t)s * (K_BYTES + V_BYTES);
-                bar_expect(&kv_full[s], K_BYTES + V_BYTES);
+            for (int j = 0; j < num_steps; ++j) {
+                const int s = j % AT_STAGES;
+                if (!bar_wait(&kv_empty[s], ((j / AT_STAGES) & 1) ^ 1, failed)) { atomicExch(p.status, 11); break; }
+                const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
+                uint8_t* dst = stage0 + (size_t)s * STAGE_BYTES;
+                bar_expect(&kv_full[s], pages * (K_BYTES + V_BYTES));
+                for (int h = 0; h < pages; ++h) {
+                    const int page = table[first_page + AT_STEP_PAGES * j + h];
+                    const int row = page * p.num_kv_heads + kvh;
 #pragma unroll
-                for (int kb = 0; kb < KBLOCKS; ++kb)
-                    tma_2d(dst + kb * (FRB_PAGE * 128), &map_k, kb * 64, (page * p.num_kv_heads + kvh) * FRB_PAGE, &kv_full[s]);
-                tma_2d(dst + K_BYTES, &map_v, 0, (page * p.num_kv_heads + kvh) * HD, &kv_full[s]);
+                    for (int kb = 0; kb < KBLOCKS; ++kb)
+                        tma_2d(dst + kb * K_BLOCK_BYTES + h * (FRB_PAGE * 128), &map_k, kb * 64, row * FRB_PAGE, &kv_full[s]);
+                    tma_2d(dst + AT_STEP_PAGES * K_BYTES + h * V_BYTES, &map_v, 0, row * HD, &kv_full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // float32 accumulate, bf16 operands, K-major; S: M 128 x N 64; O: M 128 x N HD
-            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FRB_PAGE >> 3) << 17) | ((uint32_t)(AT_QUERIES >> 4) << 24);
-            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(AT_QUERIES >> 4) << 24);
-            const uint32_t q_addr = smem_addr(q_tile);
+            // float32 accumulate, bf16 operands, K-major; S: M 128 x N 128 (64 for a step of one page); O: M 128 x N HD.
+            // An MMA of 16 along the inner size costs the tensor core about the same time whatever N up to 128:
+            // a step of two pages asks for half as many of them per key as a step of one.
+            const uint32_t idesc_common = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_QUERIES >> 4) << 24);
+            const uint32_t idesc_o = idesc_common | ((uint32_t)(HD >> 3) << 17);
+            const uint64_t q_desc = tile_desc(smem_addr(q_tile));
             bool ok = bar_wait(&q_full, 0, failed);
             if (!ok) atomicExch(p.status, 12);
-            // issues S_i = Q K_i^T into S buffer i & 1
-            auto issue_scores = [&](int i) -> bool {
-                const int s = i % AT_STAGES;
-                if (!bar_wait(&kv_full[s], (i / AT_STAGES) & 1, failed)) { atomicExch(p.status, 13); return false; }
-                if (i >= 2 && !bar_wait(&s_free[i & 1], ((i - 2) >> 1) & 1, failed)) { atomicExch(p.status, 14); return false; }
+            // issues S_j = Q K_j^T into S buffer j & 1
+            auto issue_scores = [&](int j) -> bool {
+                const int s = j % AT_STAGES;
+                if (!bar_wait(&kv_full[s], (j / AT_STAGES) & 1, failed)) { atomicExch(p.status, 13); return false; }
+                if (j >= 2 && !bar_wait(&s_free[j & 1], ((j - 2) >> 1) & 1, failed)) { atomicExch(p.status, 14); return false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t k_addr = smem_addr(stage0 + (size_t)s * (K_BYTES + V_BYTES));
+                const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
+                const uint32_t idesc_s = idesc_common | ((uint32_t)((pages * FRB_PAGE) >> 3) << 17);
+                const uint64_t k_desc = tile_desc(smem_addr(stage0 + (size_t)s * STAGE_BYTES));
 #pragma unroll
                 for (int kb = 0; kb < KBLOCKS; ++kb)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_ss(tmem + S_COL0 + 64 * (i & 1), tile_desc(q_addr + kb * (AT_QUERIES * 128) + k * 32),
-                               tile_desc(k_addr + kb * (FRB_PAGE * 128) + k * 32), idesc_s, (kb | k) != 0);
-                mma_commit(&s_full[i & 1]);
+                        mma_ss(tmem + S_COL0 + AT_STEP_KEYS * (j & 1), q_desc + ((kb * (AT_QUERIES * 128) + k * 32) >> 4),
+                               k_desc + ((kb * K_BLOCK_BYTES + k * 32) >> 4), idesc_s, (kb | k) != 0);
+                mma_commit(&s_full[j & 1]);
                 return true;
             };
             if (ok) ok = issue_scores(0);
-            for (int i = 0; i < num_pages && ok; ++i) {
-                if (i + 1 < num_pages) ok = issue_scores(i + 1);
+            for (int j = 0; j < num_steps && ok; ++j) {
+                if (j + 1 < num_steps) ok = issue_scores(j + 1);
                 if (!ok) break;
-                if (!bar_wait(&p_full[i & 1], (i >> 1) & 1, failed)) { atomicExch(p.status, 15); ok = false; break; }
+                if (!bar_wait(&p_full[j & 1], (j >> 1) & 1, failed)) { atomicExch(p.status, 15); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int s = i % AT_STAGES;
-                const uint32_t v_addr = smem_addr(stage0 + (size_t)s * (K_BYTES + V_BYTES) + K_BYTES);
+                const int s = j % AT_STAGES;
+                const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
+                const uint64_t v_desc = tile_desc(smem_addr(stage0 + (size_t)s * STAGE_BYTES + AT_STEP_PAGES * K_BYTES));
+                for (int h = 0; h < pages; ++h)
 #pragma unroll
-                for (int k = 0; k < 4; ++k)                    // 16 keys per MMA: 8 columns of packed P, 32 bytes of a V^T row
-                    mma_ts(tmem + O_COL, tmem + P_COL0 + 32 * (i & 1) + 8 * k, tile_desc(v_addr + k * 32), idesc_o, (i | k) != 0);
+                    for (int k = 0; k < 4; ++k)                // 16 keys per MMA: 8 columns of packed P, 32 bytes of a V^T row
+                        mma_ts(tmem + O_COL, tmem + P_COL0 + (AT_STEP_KEYS / 2) * (j & 1) + 32 * h + 8 * k,
+                               v_desc + ((h * V_BYTES + k * 32) >> 4), idesc_o, (j | h | k) != 0);
                 mma_commit(&kv_empty[s]);
-                mma_commit(&pv_done[i & 1]);
+                mma_commit(&pv_done[j & 1]);
             }
         }
     } else {
@@ -235,45 +260,65 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int lo = (valid && p.window > 0) ? max(0, hi - p.window + 1) : 0;
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true;
-        for (int i = 0; i < num_pages && ok; ++i) {
-            if (!bar_wait(&s_full[i & 1], (i >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 16); ok = false; break; }
+        for (int j = 0; j < num_steps && ok; ++j) {
+            if (!bar_wait(&s_full[j & 1], (j >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 16); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t raw[4][16];
+            const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
+            const int key0 = (first_page + AT_STEP_PAGES * j) * FRB_PAGE;
+            const int num_keys = pages * FRB_PAGE;
+            uint32_t raw[AT_STEP_KEYS / 16][16];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld16(lane_base + S_COL0 + 64 * (i & 1) + 16 * c, raw[c]);
+            for (int c = 0; c < AT_STEP_KEYS / 16; ++c)
+                if (16 * c < num_keys) tmem_ld16(lane_base + S_COL0 + AT_STEP_KEYS * (j & 1) + 16 * c, raw[c]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bar_arrive(&s_free[i & 1]);
-            const int key0 = (first_page + i) * FRB_PAGE;
-            float page_max = -INFINITY;
+            if (lane == 0) bar_arrive(&s_free[j & 1]);
+            // Most steps lie wholly before the tile's first query (and inside the window): no key of theirs is
+            // masked for any row of this warp, and the per-key comparisons are left out.
+            const bool open_step = __all_sync(0xffffffffu, valid && key0 + num_keys - 1 <= hi && key0 >= lo);
+            float step_max;
+            if (open_step && pages == AT_STEP_PAGES) {
+                float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains: a single one waits on itself
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < AT_STEP_KEYS / 16; ++c)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int key = key0 + 16 * c + j;
-                    const float v = (key >= lo && key <= hi) ? __uint_as_float(raw[c][j]) * p.scale2 : -INFINITY;
-                    raw[c][j] = __float_as_uint(v);
-                    page_max = fmaxf(page_max, v);
-                }
+                    for (int i = 0; i < 16; ++i) top[i & 3] = fmaxf(top[i & 3], __uint_as_float(raw[c][i]));
+                step_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;     // the scale is positive
+            } else {
+                step_max = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < AT_STEP_KEYS / 16; ++c)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int key = key0 + 16 * c + i;
+                        const bool seen = 16 * c < num_keys && key >= lo && key <= hi;
+                        const float v = seen ? __uint_as_float(raw[c][i]) : -INFINITY;
+                        raw[c][i] = __float_as_uint(v);
+                        step_max = fmaxf(step_max, v * p.scale2);
+                    }
+            }
             float corr = 1.f;
-            const bool raise = page_max > m_used + AT_RAISE;   // also true on the first page with a visible key
-            if (raise) { corr = exp2f(m_used - page_max); m_used = page_max; }
+            const bool raise = step_max > m_used + AT_RAISE;   // also true on the first step with a visible key
+            if (raise) { corr = exp2f(m_used - step_max); m_used = step_max; }
             const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-            float sum = 0.f;
-            uint32_t packed[2][16];
+            float sums[2] = {0.f, 0.f};
+            uint32_t packed[AT_STEP_KEYS / 32][16];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < AT_STEP_KEYS / 16; ++c)
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    const float a = exp2f(__uint_as_float(raw[c][j]) - m_sub), bb = exp2f(__uint_as_float(raw[c][j + 1]) - m_sub);
-                    sum += a + bb;
-                    packed[c >> 1][(c & 1) * 8 + (j >> 1)] = pack2(a, bb);
+                for (int i = 0; i < 16; i += 2) {
+                    // 2^(s * scale - m): one multiply-add and the hardware's exponential (a masked key gives 2^-inf = 0)
+                    const float a = exp2_fast(fmaf(__uint_as_float(raw[c][i]), p.scale2, -m_sub));
+                    const float bb = exp2_fast(fmaf(__uint_as_float(raw[c][i + 1]), p.scale2, -m_sub));
+                    sums[0] += a;
+                    sums[1] += bb;
+                    packed[c >> 1][(c & 1) * 8 + (i >> 1)] = pack2(a, bb);
                 }
-            l_sum = l_sum * corr + sum;
-            if (i >= 2 && !bar_wait(&pv_done[i & 1], ((i - 2) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 17); ok = false; break; }
-            if (i > 0 && __any_sync(0xffffffffu, raise)) {     // rare: O must follow the new maximum
-                if (!bar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 18); ok = false; break; }
+            l_sum = l_sum * corr + (sums[0] + sums[1]);
+            if (j >= 2 && !bar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 17); ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {     // rare: O must follow the new maximum
+                if (!bar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 18); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int c = 0; c < HD / 16; ++c) {
@@ -281,19 +326,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tmem_ld16(lane_base + O_COL + 16 * c, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
                     tmem_st16(lane_base + O_COL + 16 * c, o);
                 }
             }
-            tmem_st16(lane_base + P_COL0 + 32 * (i & 1), packed[0]);
-            tmem_st16(lane_base + P_COL0 + 32 * (i & 1) + 16, packed[1]);
+#pragma unroll
+            for (int c = 0; c < AT_STEP_KEYS / 32; ++c)
+                if (32 * c < num_keys) tmem_st16(lane_base + P_COL0 + (AT_STEP_KEYS / 2) * (j & 1) + 16 * c, packed[c]);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bar_arrive(&p_full[i & 1]);
+            if (lane == 0) bar_arrive(&p_full[j & 1]);
         }
         if (ok) {
-            const int last = num_pages - 1;
+            const int last = num_steps - 1;
             if (!bar_wait(&pv_done[last & 1], (last >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
         }
         if (ok) {
@@ -373,6 +419,7 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
                                      int window, int* status, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(head_dim == 64 || head_dim == 128, "tensor-core attention: head_dim %d is neither 64 nor 128", head_dim);
+    FRB_CHECK_ARG(scale > 0.f, "tensor-core attention: a softmax scale of %g is not positive", (double)scale);
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && num_heads <= 65535, "tensor-core attention: %d heads over %d kv heads",
                   num_heads, num_kv_heads);
     CUtensorMap map_q, map_k, map_v;
@@ -386,7 +433,7 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
     p.seq_q_len = seq_q_len; p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.status = status;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads;
-    const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
+    const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * AT_STEP_PAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
     dim3 grid(num_tiles, num_heads);
     if (head_dim == 128) {
         cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

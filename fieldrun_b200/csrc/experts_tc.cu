@@ -115,13 +115,16 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __shared__ uint64_t full_bar[8], empty_bar[8], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
-    const int tile = blockIdx.x;
+    // blocks that follow one another take the feature blocks of one tile: they read the same rows (which stay
+    // in L2) and, where an expert has several tiles, the blocks of its next tile read the same weights soon after
+    const int feature_blocks = p.F / TC_FEATS;
+    const int tile = blockIdx.x / feature_blocks;
     if (tile >= p.num_tiles[0]) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = p.tile_expert[tile];
     const int row0 = p.tile_row0[tile];
     const int rows = min(p.NT, p.offsets[e + 1] - row0);
-    const int f0 = blockIdx.y * TC_FEATS;
+    const int f0 = (blockIdx.x - tile * feature_blocks) * TC_FEATS;
     const int f_total = PAIRED ? 2 * p.F : p.F;
     const int w_row_gate = e * f_total + f0, w_row_up = w_row_gate + p.F;
     const int k_blocks = p.K / TC_KBLOCK;
@@ -273,8 +276,9 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
     int stages = (int)(((two_per_sm ? 110 : 200) * 1024) / stage_bytes);
     p.stages = stages > 8 ? 8 : stages;
     const size_t smem = p.stages * stage_bytes + 1024;
-    dim3 grid(max_tiles, F / TC_FEATS);
-    FRB_CHECK_ARG(grid.y <= 65535, "expert tensor-core product: %d features exceed the grid", F);
+    FRB_CHECK_ARG((long long)max_tiles * (F / TC_FEATS) < (1ll << 31), "expert tensor-core product: %d tiles of %d features exceed the grid",
+                  max_tiles, F);
+    dim3 grid((unsigned)max_tiles * (F / TC_FEATS));
     if (paired) {
         cudaFuncSetAttribute(expert_gemm_tc_kernel<true, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         expert_gemm_tc_kernel<true, bf16><<<grid, TC_THREADS, smem, stream>>>(map_w, map_x, p);

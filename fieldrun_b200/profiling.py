@@ -5,10 +5,11 @@ profilers.
 
 Each case holds between a few hundred MB and 2 GB on the device (more than the L2 cache, far less than a model), runs a few
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
-arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05),
+arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05: 64 rows per expert), ``experts_tc_large`` (512 rows
+per expert, as in a step of 16k prompt tokens),
 ``experts_stream`` (decode-sized expert products, streamed), ``attention_decode`` (pages by TMA),
 ``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
-(mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries),
+(mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries; ``attention_prefill_tc_long``: one prompt of 16,384 tokens),
 ``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
 this library's own.
@@ -68,8 +69,8 @@ def _expert_lists(rows_per_expert: list[int], tile_rows: int, device):
 def experts(kind: str, launches: int) -> dict:
     dev = torch.device("cuda")
     experts_n = 64
-    rows_per = [64] * experts_n if kind == "tc" else [1, 2] * (experts_n // 2)
-    tile_rows = 128 if kind == "tc" else 8
+    rows_per = {"tc": [64] * experts_n, "tc_large": [512] * experts_n}.get(kind, [1, 2] * (experts_n // 2))
+    tile_rows = {"tc": 128, "tc_large": 256}.get(kind, 8)
     n = sum(rows_per)
     w13 = (torch.randn(experts_n, 2 * WIDTH, HIDDEN, device=dev) * 0.02).to(torch.bfloat16)
     w2 = (torch.randn(experts_n, HIDDEN, WIDTH, device=dev) * 0.02).to(torch.bfloat16)
@@ -79,7 +80,7 @@ def experts(kind: str, launches: int) -> dict:
     tile_expert, tile_row0, num_tiles, offsets, tiles = _expert_lists(rows_per, tile_rows, dev)
 
     def launch():
-        if kind == "tc":
+        if kind.startswith("tc"):
             ops.expert_gemm_tc(w13, x, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True)
             ops.expert_gemm_tc(w2, hidden, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False)
         else:
@@ -89,17 +90,17 @@ def experts(kind: str, launches: int) -> dict:
                                 **ops.stream_shape(tiles, HIDDEN, WIDTH, tile_rows))
 
     ms = _time(launch, launches)
-    if kind == "tc":
+    if kind.startswith("tc"):
         ops.tc_status_check(dev)
     weight_bytes = (w13.numel() + w2.numel()) * 2
     flops = 2 * n * 3 * WIDTH * HIDDEN
-    return {"case": f"experts_{'tc' if kind == 'tc' else 'stream'}", "ms": round(ms, 4), "experts": experts_n, "rows": n,
+    return {"case": f"experts_{kind}", "ms": round(ms, 4), "experts": experts_n, "rows": n,
             "weight_gb_per_s": round(weight_bytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 2)}
 
 
 def attention(kind: str, launches: int) -> dict:
     dev = torch.device("cuda")
-    batch, context = (32, 4096) if kind.startswith("decode") else (1, 2048)
+    batch, context = (32, 4096) if kind.startswith("decode") else (1, 16384 if kind.endswith("_long") else 2048)
     pages_per = context // 64
     pages = batch * pages_per
     keys = (torch.randn(pages, KV_HEADS, 64, HEAD_DIM, device=dev) * 0.3).to(torch.bfloat16)
@@ -130,7 +131,7 @@ def attention(kind: str, launches: int) -> dict:
     zero = torch.zeros(1, dtype=torch.int32, device=dev)
     q_len = torch.tensor([context], dtype=torch.int32, device=dev)
     cu = torch.tensor([0, context], dtype=torch.int32, device=dev)
-    if kind == "prefill_tc":
+    if kind.startswith("prefill_tc"):
         tile_seq = torch.zeros(context // 128, dtype=torch.int32, device=dev)
         tile_q0 = torch.arange(0, context, 128, dtype=torch.int32, device=dev)
         launch = lambda: ops.attention_prefill_tc(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
@@ -139,7 +140,7 @@ def attention(kind: str, launches: int) -> dict:
         launch = lambda: ops.attention_prefill_mma(q, keys, values, table, tile_seq, tile_q0, zero, zero, q_len, cu, out,
                                                    num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM, scale=scale, window=None)
     ms = _time(launch, launches)
-    if kind == "prefill_tc":
+    if kind.startswith("prefill_tc"):
         ops.tc_status_check(dev)
     flops = 4 * HEADS * HEAD_DIM * context * (context + 1) // 2
     return {"case": f"attention_{kind}", "ms": round(ms, 4), "tokens": context, "tflops": round(flops / ms / 1e9, 2)}
@@ -203,11 +204,13 @@ def small_kernels(launches: int, tokens: int) -> dict:
 
 CASES = {
     "experts_tc": lambda n: experts("tc", n),
+    "experts_tc_large": lambda n: experts("tc_large", n),
     "experts_stream": lambda n: experts("stream", n),
     "attention_decode": lambda n: attention("decode", n),
     "attention_decode_mma": lambda n: attention("decode_mma", n),
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
+    "attention_prefill_tc_long": lambda n: attention("prefill_tc_long", n),
     "decode_small_kernels": lambda n: small_kernels(n, 8),
     "prefill_small_kernels": lambda n: small_kernels(n, 2048),
 }
