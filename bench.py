@@ -263,8 +263,15 @@ def main() -> int:
         per_layer = (2 * PROMPT * d * (nh + 2 * nkv) * hd + 4 * nh * hd * PROMPT * (PROMPT + 1) // 2 + 2 * PROMPT * nh * hd * d
                      + 2 * PROMPT * d * cfg.num_local_experts + 2 * PROMPT * cfg.num_experts_per_tok * 3 * cfg.intermediate_size * d)
         flops = per_layer * args.layers + 2 * d * cfg.vocab_size
+        # 2,048 tokens with 8 picks each reach every expert of a layer, so the prompt has to read all weights once:
+        # that, not the arithmetic, bounds the step.  "hbm_frac" is those bytes / time / the HBM peak.
+        layer_bytes = (((nh + 2 * nkv) * hd * d + nh * hd * d) * 2 + cfg.num_local_experts * d * 4
+                       + cfg.num_local_experts * 3 * cfg.intermediate_size * d * 2)
+        prefill_bytes = layer_bytes * args.layers + d * cfg.vocab_size * 2
         result["prefill"] = {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
-                             "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "flops": flops}
+                             "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "flops": flops,
+                             "weight_bytes": prefill_bytes,
+                             "hbm_frac": round(prefill_bytes / (prefill_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
         # ---- decode at batch 1 and 64 ------------------------------------------------------------------------
         points = {}
         for batch in (1, 64):
