@@ -10,7 +10,8 @@ per expert, as in a step of 16k prompt tokens),
 ``experts_stream`` (decode-sized expert products, streamed), ``attention_decode`` (pages by TMA),
 ``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
 (mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries; ``attention_prefill_tc_long``: one prompt of 16,384 tokens),
-``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens).
+``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens),
+``step_decode`` and ``step_prefill`` (two whole layers through the engine, for launch lists; not part of ``all``).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
 this library's own.
 """
@@ -202,6 +203,54 @@ def small_kernels(launches: int, tokens: int) -> dict:
     return out
 
 
+def whole_step(kind: str, launches: int) -> dict:
+    """Two layers of MiniMax-M2's sizes stepped through the engine: ``step_decode`` runs `launches` decode steps
+    of 8 sequences over 2,048-token contexts, ``step_prefill`` one prompt of 2,048 tokens `launches` times.  The
+    measured steps lie between cudaProfilerStart and cudaProfilerStop, so that
+    ``ncu --profile-from-start off --metrics gpu__time_duration.sum`` lists their kernels and nothing else."""
+    from . import RandomInit, random_model
+    config = {"architectures": ["MiniMaxM2ForCausalLM"], "hidden_size": HIDDEN, "num_hidden_layers": 2,
+              "num_attention_heads": HEADS, "num_key_value_heads": KV_HEADS, "head_dim": HEAD_DIM, "rotary_dim": 64,
+              "rope_theta": 5e6, "use_qk_norm": True, "num_local_experts": 256, "num_experts_per_tok": 8,
+              "intermediate_size": WIDTH, "vocab_size": 200064, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    batch, prompt = (8, 2048) if kind == "decode" else (1, 2048)
+    lm = random_model(config, RandomInit(seed=2, bias_std=0.01), dtype="bfloat16", max_tokens=(batch + 1) * (prompt + 128),
+                      num_slots=batch + 1)
+    engine = lm.engine
+    engine.record_steps = False                      # run directly: every kernel is a launch of its own
+    rng = np.random.default_rng(0)
+    prompts = lambda n: [rng.integers(0, 200064, size=prompt).tolist() for _ in range(n)]
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if kind == "decode":
+        slots = [engine.new_sequence() for _ in range(batch)]
+        tokens = engine.pick(engine.step(slots, prompts(batch)))
+        for _ in range(3):
+            tokens = engine.pick(engine.step(slots, [[t] for t in tokens]))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        begin.record()
+        for _ in range(launches):
+            tokens = engine.pick(engine.step(slots, [[t] for t in tokens]))
+        end.record()
+    else:
+        for _ in range(2):
+            slot = engine.new_sequence()
+            engine.step([slot], prompts(1))
+            engine.release(slot)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        begin.record()
+        for _ in range(launches):
+            slot = engine.new_sequence()
+            engine.step([slot], prompts(1))
+            engine.release(slot)
+        end.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return {"case": f"step_{kind}", "layers": 2, "batch": batch, "context": prompt,
+            "ms_per_step_with_host": round(begin.elapsed_time(end) / launches, 3)}
+
+
 CASES = {
     "experts_tc": lambda n: experts("tc", n),
     "experts_tc_large": lambda n: experts("tc_large", n),
@@ -211,6 +260,8 @@ CASES = {
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
     "attention_prefill_tc_long": lambda n: attention("prefill_tc_long", n),
+    "step_decode": lambda n: whole_step("decode", n),
+    "step_prefill": lambda n: whole_step("prefill", n),
     "decode_small_kernels": lambda n: small_kernels(n, 8),
     "prefill_small_kernels": lambda n: small_kernels(n, 2048),
 }
@@ -224,7 +275,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         raise SystemExit("fieldrun_b200.profiling needs a CUDA device")
     torch.manual_seed(0)
-    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+    for name in ([c for c in sorted(CASES) if not c.startswith("step_")] if args.case == "all" else [args.case]):
         print(json.dumps(CASES[name](args.launches)))
     return 0
 
