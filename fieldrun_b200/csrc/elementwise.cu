@@ -47,6 +47,24 @@ FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype
     FRB_RETURN_LAUNCH("embed_rows");
 }
 
+// Four neighbouring elements at once.
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned int*>(&lo);
+    raw.y = *reinterpret_cast<const unsigned int*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ----------------------------------------------------------------------------- RMSNorm (+ residual add)
 
 // Rows are one block each.  A step of few rows takes blocks of 1024 threads (the row's latency is the step's);
@@ -67,13 +85,13 @@ struct ExpertSum {
 // One block per output row r.  src = rows ? rows[r] : r.  v = x[src] (+ delta[src]) (+ the experts' sum of
 // src); if write_back the sum is stored to x[src] (the residual stream).
 // out[r] = v * (1/sqrt(mean(v^2)+eps)) * w, in OutT and, when out32 is given, in float32 as well.
-template <typename OutT, typename WT, int NORM_BLOCK>
+template <typename OutT, typename WT, int NORM_BLOCK, bool VEC>
 __global__ void __launch_bounds__(NORM_BLOCK)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum experts, const int* __restrict__ rows,
                const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
                int write_back) {
     after_previous_kernel();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     __shared__ float expert_weight[NORM_MAX_TOP_K];
     __shared__ const float* expert_row[NORM_MAX_TOP_K];
@@ -90,24 +108,64 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum
         __syncthreads();
     }
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
-        float v = xr[i];
-        if (dr) v += dr[i];
-        if (experts.y) {
-            float sum = 0.f;
-            for (int k = 0; k < experts.top_k; ++k) sum += expert_weight[k] * expert_row[k][i];
-            v += sum;
+    if (VEC) {
+        // four elements at a time; a token's expert rows are loaded together, then added in rank order
+        for (int i = 4 * threadIdx.x; i < width; i += 4 * NORM_BLOCK) {
+            float4 v = *reinterpret_cast<const float4*>(xr + i);
+            if (dr) {
+                const float4 d = *reinterpret_cast<const float4*>(dr + i);
+                v = make_float4(v.x + d.x, v.y + d.y, v.z + d.z, v.w + d.w);
+            }
+            if (experts.y) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int k0 = 0; k0 < experts.top_k; k0 += 8) {
+                    float4 part[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (k0 + k < experts.top_k) part[k] = *reinterpret_cast<const float4*>(expert_row[k0 + k] + i);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (k0 + k < experts.top_k) {
+                            const float w = expert_weight[k0 + k];
+                            sum = make_float4(sum.x + w * part[k].x, sum.y + w * part[k].y, sum.z + w * part[k].z, sum.w + w * part[k].w);
+                        }
+                }
+                v = make_float4(v.x + sum.x, v.y + sum.y, v.z + sum.z, v.w + sum.w);
+            }
+            *reinterpret_cast<float4*>(row + i) = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            if (write_back) *reinterpret_cast<float4*>(xr + i) = v;
         }
-        row[i] = v;
-        ss += v * v;
-        if (write_back) xr[i] = v;
+    } else {
+        for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
+            float v = xr[i];
+            if (dr) v += dr[i];
+            if (experts.y) {
+                float sum = 0.f;
+                for (int k = 0; k < experts.top_k; ++k) sum += expert_weight[k] * expert_row[k][i];
+                v += sum;
+            }
+            row[i] = v;
+            ss += v * v;
+            if (write_back) xr[i] = v;
+        }
     }
     ss = block_sum<NORM_BLOCK>(ss, scratch);
     const float rinv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
-        const float y = row[i] * rinv * to_f32<WT>(weight[i]);
-        out[(size_t)r * width + i] = from_f32<OutT>(y);
-        if (out32) out32[(size_t)r * width + i] = y;
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < width; i += 4 * NORM_BLOCK) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            const float4 w = load4<WT>(weight + i);
+            const float4 y = make_float4(v.x * rinv * w.x, v.y * rinv * w.y, v.z * rinv * w.z, v.w * rinv * w.w);
+            store4<OutT>(out + (size_t)r * width + i, y);
+            if (out32) *reinterpret_cast<float4*>(out32 + (size_t)r * width + i) = y;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += NORM_BLOCK) {
+            const float y = row[i] * rinv * to_f32<WT>(weight[i]);
+            out[(size_t)r * width + i] = from_f32<OutT>(y);
+            if (out32) out32[(size_t)r * width + i] = y;
+        }
     }
 }
 
@@ -121,17 +179,19 @@ FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, con
     ExpertSum experts = {expert_y, expert_weights, row_of_assign, top_k};
     const size_t smem = (size_t)width * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "rmsnorm: width %d needs %zu bytes of shared memory, more than 200 KB", width, smem);
+    const auto on16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
+    const bool by_four = width % 4 == 0 && on16(x) && on16(delta) && on16(expert_y) && on16(out) && on16(out32) && on16(weight);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
         if (num_rows <= NORM_FEW_ROWS) {
-            auto kernel = rmsnorm_kernel<OutT, WT, 1024>;
+            auto kernel = by_four ? rmsnorm_kernel<OutT, WT, 1024, true> : rmsnorm_kernel<OutT, WT, 1024, false>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            launch_dependent(kernel, dim3(num_rows), dim3(1024), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
-                                                     write_back);
+            launch_dependent(kernel, dim3(num_rows), dim3(1024), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width,
+                             (OutT*)out, out32, write_back);
         } else {
-            auto kernel = rmsnorm_kernel<OutT, WT, 256>;
+            auto kernel = by_four ? rmsnorm_kernel<OutT, WT, 256, true> : rmsnorm_kernel<OutT, WT, 256, false>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            launch_dependent(kernel, dim3(num_rows), dim3(256), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width, (OutT*)out, out32,
-                                                    write_back);
+            launch_dependent(kernel, dim3(num_rows), dim3(256), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width,
+                             (OutT*)out, out32, write_back);
         }
     }));
     FRB_RETURN_LAUNCH("rmsnorm");
@@ -153,6 +213,7 @@ struct QkvParams {
     void* v_pages;            // [pages, nkv, hd, PAGE] OutT: values lie transposed within a page
     float eps;
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
+    int num_tokens, v_tiles;  // v_tiles: blocks beyond the tokens' own write the values, 64 tokens of one kv head each
 };
 
 #define QKV_BATCH 8          // elements a thread loads before it uses any of them
@@ -243,25 +304,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     }
 }
 
-// Four neighbouring elements at once.
-template <typename T> __device__ __forceinline__ float4 load4(const T* p);
-template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
-template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
-}
-template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
-template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-    uint2 raw;
-    raw.x = *reinterpret_cast<const unsigned int*>(&lo);
-    raw.y = *reinterpret_cast<const unsigned int*>(&hi);
-    *reinterpret_cast<uint2*>(p) = raw;
-}
-
 #define QKV_VEC_BATCH 4      // groups of four elements a thread loads before it uses any of them
+#define QKV_V_TOKENS 64      // tokens whose values one block transposes
 
 // The same work four elements at a time, for head sizes and rotation widths in steps of four (eight for the
 // half-split pairing, so that a group's partners are a group too) and rows that start on 16 bytes.
@@ -270,10 +314,37 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     after_previous_kernel();
     extern __shared__ __align__(16) float raw[];   // Q row, K row, V row; then cos and sin [rotary_dim / 2]
     __shared__ float scratch[32];
-    const int t = blockIdx.x;
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
     const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    if (blockIdx.x >= p.num_tokens) {
+        // The values of 64 tokens of one kv head: read along the dimensions, written along the tokens, whose
+        // places in a transposed page are neighbours whenever their positions are (a prompt's are).
+        __shared__ int s_page[QKV_V_TOKENS], s_place[QKV_V_TOKENS];
+        OutT* tile = reinterpret_cast<OutT*>(raw);                       // [hd][QKV_V_TOKENS + 2]
+        const int index = blockIdx.x - p.num_tokens;
+        const int h = index % p.num_kv_heads, t0 = (index / p.num_kv_heads) * QKV_V_TOKENS;
+        const int count = min(QKV_V_TOKENS, p.num_tokens - t0);
+        for (int j = threadIdx.x; j < count; j += NORM_BLOCK) {
+            const int pos = p.tok_pos[t0 + j];
+            s_page[j] = p.page_table[(size_t)p.tok_slot[t0 + j] * p.max_pages + pos / FRB_PAGE];
+            s_place[j] = pos % FRB_PAGE;
+        }
+        for (int i = threadIdx.x; i < count * hd; i += NORM_BLOCK) {
+            const int j = i / hd, d = i - j * hd;
+            const InT* row = (const InT*)p.qkv + (size_t)(t0 + j) * all_width + qk_width + h * hd;
+            tile[d * (QKV_V_TOKENS + 2) + j] = from_f32<OutT>(to_f32<InT>(row[d]));
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < count * hd; i += NORM_BLOCK) {
+            const int d = i / count, j = i - d * count;
+            const size_t at = (((size_t)s_page[j] * p.num_kv_heads + h) * hd + d) * FRB_PAGE + s_place[j];
+            ((OutT*)p.v_pages)[at] = tile[d * (QKV_V_TOKENS + 2) + j];
+        }
+        return;
+    }
+    const int t = blockIdx.x;
+    const int row_width = p.v_tiles ? qk_width : all_width;               // the values are other blocks' work then
     const int half = p.rotary_dim / 2;
     float* s_cos = raw + all_width;
     float* s_sin = s_cos + half;
@@ -284,12 +355,12 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     const int pos = p.tok_pos[t];
     const int slot = p.tok_slot[t];
     float ssq = 0.f, ssk = 0.f;
-    for (int base = 0; base < all_width; base += 4 * QKV_VEC_BATCH * NORM_BLOCK) {
+    for (int base = 0; base < row_width; base += 4 * QKV_VEC_BATCH * NORM_BLOCK) {
         float4 v[QKV_VEC_BATCH], w[QKV_VEC_BATCH];
 #pragma unroll
         for (int u = 0; u < QKV_VEC_BATCH; ++u) {
             const int i = base + 4 * (u * NORM_BLOCK + threadIdx.x);
-            v[u] = i < all_width ? load4<InT>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[u] = i < row_width ? load4<InT>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             w[u] = make_float4(1.f, 1.f, 1.f, 1.f);
             if (i < q_width) { if (qw) w[u] = load4<WT>(qw + i); }
             else if (i < qk_width) { if (kw) w[u] = load4<WT>(kw + i - q_width); }
@@ -297,7 +368,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
 #pragma unroll
         for (int u = 0; u < QKV_VEC_BATCH; ++u) {
             const int i = base + 4 * (u * NORM_BLOCK + threadIdx.x);
-            if (i < all_width)
+            if (i < row_width)
                 *reinterpret_cast<float4*>(raw + i) = make_float4(v[u].x * w[u].x, v[u].y * w[u].y, v[u].z * w[u].z, v[u].w * w[u].w);
             const float ss = v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
             if (i < q_width) ssq += ss;
@@ -347,7 +418,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
             store4<OutT>((OutT*)p.k_pages + at, a);
         }
     }
-    if (page >= 0) {
+    if (page >= 0 && !p.v_tiles) {
         const float* vrow = raw + qk_width;
         for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
             const int head = i / hd, dim = i - head * hd;
@@ -373,6 +444,7 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.v_pages = v_pages; p.eps = eps; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
     p.rotary_dim = rotary_dim; p.interleaved = interleaved; p.max_pages = max_pages; p.write_cache = write_cache;
     p.table_positions = table_positions;
+    p.num_tokens = num_tokens; p.v_tiles = 0;
     const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim) * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + 2 kv heads) * head_dim = %d needs more than 200 KB of shared memory",
                   (num_heads + 2 * num_kv_heads) * head_dim);
@@ -386,6 +458,16 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
             auto kernel = by_four ? qkv_prepare_vec_kernel<InT, OutT, WT, 1024> : qkv_prepare_kernel<InT, OutT, WT, 1024>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             launch_dependent(kernel, dim3(num_tokens), dim3(1024), smem, stream, p);
+        } else if (by_four && write_cache) {
+            // many tokens: the values go through blocks of their own (64 tokens of a kv head), which write them
+            // along the tokens instead of one two-byte store per token and dimension
+            p.v_tiles = 1;
+            const size_t tile_bytes = (size_t)head_dim * (QKV_V_TOKENS + 2) * sizeof(OutT);
+            const size_t bytes = smem > tile_bytes ? smem : tile_bytes;
+            auto kernel = qkv_prepare_vec_kernel<InT, OutT, WT, 256>;
+            if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            const int v_blocks = (num_tokens + QKV_V_TOKENS - 1) / QKV_V_TOKENS * num_kv_heads;
+            launch_dependent(kernel, dim3(num_tokens + v_blocks), dim3(256), bytes, stream, p);
         } else {
             auto kernel = by_four ? qkv_prepare_vec_kernel<InT, OutT, WT, 256> : qkv_prepare_kernel<InT, OutT, WT, 256>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

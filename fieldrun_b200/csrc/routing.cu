@@ -218,17 +218,18 @@ __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_fill_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int top_k, const int* __restrict__ counts,
                  int* __restrict__ sorted_token, int* __restrict__ row_of_assign) {
     extern __shared__ int next_place[];          // [E]
-    __shared__ int place[PLAN_CHUNK];
+    __shared__ int place[PLAN_CHUNK];            // first the chunk's expert ids (all threads fetch them), then their places
     const int c = blockIdx.x;
     const int begin = c * PLAN_CHUNK, n = min(num_assign - begin, PLAN_CHUNK);
     for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) next_place[e] = counts[(size_t)c * num_experts + e];
+    for (int i = threadIdx.x; i < n; i += PLAN_BLOCK) place[i] = ids[begin + i];
     __syncthreads();
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         for (int base = 0; base < n; base += 32) {
             const int i = base + lane;
             const bool live = i < n;
-            const int e = live ? ids[begin + i] : -1 - lane;             // idle lanes match nobody
+            const int e = live ? place[i] : -1 - lane;                   // idle lanes match nobody
             const unsigned same = __match_any_sync(0xffffffffu, e);
             const int rank = __popc(same & ((1u << lane) - 1));
             if (live) place[i] = next_place[e] + rank;

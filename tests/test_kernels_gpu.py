@@ -53,7 +53,7 @@ def test_embedding_rows(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [100, 3072, 5000])
+@pytest.mark.parametrize("width", [100, 1001, 3072, 5000])
 def test_rmsnorm_with_residual_sum_rows_and_float32_copy(dtype, width):
     rng = np.random.default_rng(1)
     x, delta, w = rng.normal(size=(9, width)), rng.normal(size=(9, width)), 1 + 0.1 * rng.normal(size=width)
@@ -637,9 +637,9 @@ def test_router_logits_choice_and_lists_in_one_launch(tokens, top_k, experts, wi
             assert torch.equal(a[name][:nt], b[name][:nt]), name
 
 
-def test_norm_adds_the_experts_outputs_in_rank_order():
+@pytest.mark.parametrize("tokens,top_k,width", [(9, 3, 200), (70, 9, 201), (70, 9, 204)])
+def test_norm_adds_the_experts_outputs_in_rank_order(tokens, top_k, width):
     rng = np.random.default_rng(20)
-    tokens, top_k, width = 9, 3, 200
     x = rng.normal(size=(tokens, width)).astype(np.float32)
     y = rng.normal(size=(tokens * top_k, width)).astype(np.float32)
     ew = rng.random(size=(tokens, top_k)).astype(np.float32)
