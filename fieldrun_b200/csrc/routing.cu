@@ -18,7 +18,7 @@ __device__ __forceinline__ unsigned int ordered_bits(float v) {
 #define PICK_PER_LANE 8      // experts a lane keeps in registers: up to 256 experts on the fast path
 
 // One warp picks one token's experts.  z: the token's E logits; score/choice: E floats of scratch each.
-// Each lane owns the experts lane, lane + 32, ...; a round finds the largest choice value in the warp (ties:
+// Each lane owns the experts lane, lane + 32, ...; a pass finds the largest choice value in the warp (ties:
 // the lowest expert id, as a stable sort would), hands it out and removes it.
 __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const float* __restrict__ bias, int num_experts,
                                              int top_k, int renormalize, float routed_scale, float* score, float* choice,
