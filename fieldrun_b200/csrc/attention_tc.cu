@@ -208,8 +208,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     } else if (warp == 1) {
         if (lane == 0) {
             // float32 accumulate, bf16 operands, K-major; S: M 128 x N 128 (64 for a step of one page); O: M 128 x N HD.
-            // An MMA of 16 along the inner size costs the tensor core about the same time whatever N up to 128:
-            // a step of two pages asks for half as many of them per key as a step of one.
+            // An MMA of 16 along the inner size takes the tensor core about 130 cycles whatever N up to 128 (clock
+            // stamps around the issue; a second issuing thread changes nothing): a step of two pages asks for half
+            // as many of them per key as a step of one.
             const uint32_t idesc_common = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_QUERIES >> 4) << 24);
             const uint32_t idesc_o = idesc_common | ((uint32_t)(HD >> 3) << 17);
             const uint64_t q_desc = tile_desc(smem_addr(q_tile));
