@@ -41,10 +41,13 @@ def peaks() -> tuple[dict, str]:
             with open(path) as handle:
                 data = json.load(handle)
             out = dict(FALLBACK_PEAKS)
+            found = 0
             for key in out:
-                if isinstance(data.get(key), (int, float)):
+                if isinstance(data.get(key), (int, float)) and data[key] > 0:
                     out[key] = float(data[key])
-            return out, "measured"
+                    found += 1
+            if found:
+                return out, "measured" if found == len(out) else "measured where given, else fallback"
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
