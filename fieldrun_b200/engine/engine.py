@@ -82,6 +82,8 @@ class Engine:
         self.record_steps = record_steps and model.replayable
         self._recorded: dict[tuple[int, int], _RecordedStep] = {}
         self.steps_replayed = 0
+        # most prompt tokens that the generation loop puts into one step (a step's buffers grow with its tokens)
+        self.prompt_tokens_per_step = 16384
 
     # -- sequences -------------------------------------------------------------------------------------
     def new_sequence(self) -> int:

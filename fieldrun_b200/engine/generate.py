@@ -1,6 +1,8 @@
 """The generation loop above the step function.
 
-Requests are taken in order into batches; a batch's prompts run in one step,
+Requests are taken in order into batches; a batch's prompts run in one step (in
+several when together they pass ``PROMPT_TOKENS_PER_STEP``, so that a step's buffers stay
+bounded: a batch of 64 prompts of 2,048 tokens would otherwise need tens of GB of them),
 then every live sequence gets one token per step; a sequence that ends leaves
 the following steps; when the batch is done its slots go back and the next batch
 uses them.  Per sequence the rules are the reference's stream loop
@@ -40,6 +42,26 @@ class Generated:
 
 class GenerationError(ValueError):
     pass
+
+
+PROMPT_TOKENS_PER_STEP = 16384      # most prompt tokens in one step, unless a single prompt is longer
+
+
+def prompt_steps(lengths: Sequence[int], budget: int) -> list[list[int]]:
+    """Cut a batch's prompts, in order, into steps of at most ``budget`` tokens (a longer prompt goes alone).
+    Returns lists of positions in ``lengths``."""
+    steps: list[list[int]] = []
+    current: list[int] = []
+    held = 0
+    for position, n in enumerate(lengths):
+        if current and held + n > budget:
+            steps.append(current)
+            current, held = [], 0
+        current.append(position)
+        held += n
+    if current:
+        steps.append(current)
+    return steps
 
 
 def tokens_reserved(request: Request) -> int:
@@ -84,11 +106,21 @@ def run_batch(engine, batch: Sequence[Request], emit: Optional[Callable[[int, in
         return results
     slots = {b: engine.new_sequence() for b in live}
     try:
-        logits = engine.step([slots[b] for b in live], [list(batch[b].prompt) for b in live])
+        def pick(members, logits):
+            temperatures = [batch[b].temperature for b in members]
+            uniforms = [uniform(batch[b].seed, batch[b].index, len(results[b].tokens)) for b in members]
+            return engine.pick(logits, temperatures, uniforms)
+
+        # the prompts: one step, or several when they are many tokens; the first tokens are picked step by step
+        budget = getattr(engine, "prompt_tokens_per_step", PROMPT_TOKENS_PER_STEP)
+        picked: list[int] = []
+        for members in prompt_steps([len(batch[b].prompt) for b in live], budget):
+            group = [live[i] for i in members]
+            picked += pick(group, engine.step([slots[b] for b in group], [list(batch[b].prompt) for b in group]))
+        logits = None
         while live:
-            temperatures = [batch[b].temperature for b in live]
-            uniforms = [uniform(batch[b].seed, batch[b].index, len(results[b].tokens)) for b in live]
-            picked = engine.pick(logits, temperatures, uniforms)
+            if logits is not None:
+                picked = pick(live, logits)
             still: list[int] = []
             feed: list[list[int]] = []
             for b, token in zip(live, picked):

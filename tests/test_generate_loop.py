@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from fieldrun_b200.engine.generate import (GenerationError, Request, generate, plan_batches, run_batch,
+from fieldrun_b200.engine.generate import (GenerationError, Request, generate, plan_batches, prompt_steps, run_batch,
                                            tokens_reserved)
 from fieldrun_b200.sampling import uniform
 
@@ -159,3 +159,18 @@ def test_sampling_is_per_request_not_per_batch_position():
     assert [r.tokens for r in together] == [r.tokens for r in alone]
     other_seed = generate(ScriptedEngine(), [Request(r.prompt, 6, 1.5, 4, index=r.index) for r in reqs])
     assert [r.tokens for r in other_seed] != [r.tokens for r in together]
+
+
+def test_many_prompt_tokens_are_run_in_several_steps():
+    assert prompt_steps([5, 5, 5], 10) == [[0, 1], [2]]
+    assert prompt_steps([50, 1, 1], 10) == [[0], [1, 2]]          # a prompt above the budget goes alone
+    assert prompt_steps([3], 10) == [[0]]
+    engine = ScriptedEngine()
+    engine.prompt_tokens_per_step = 10
+    prompts = [[1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11], [12, 13], [14] * 12]
+    requests = [Request(tuple(p), 4, index=i) for i, p in enumerate(prompts)]
+    results = run_batch(engine, requests)
+    assert engine.steps[:3] == [[6], [5, 2], [12]]                 # three prompt steps, then all four decode together
+    assert engine.steps[3] == [1, 1, 1, 1]
+    for p, r in zip(prompts, results):
+        assert r.tokens == expected(p, 4)
