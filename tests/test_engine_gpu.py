@@ -225,17 +225,19 @@ M2_SHAPED = dict(
     tie_word_embeddings=False)
 
 
-def test_a_layer_of_minimax_m2_size():
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_a_layer_of_minimax_m2_size(dtype):
     """One layer with MiniMax-M2's own sizes (48 heads over 8, head size 128 with 64 rotary dims, q/k norms
     6,144 and 1,024 wide, experts 3,072 x 1,536, top 8; fewer experts and a small vocabulary keep the folder
-    small): a prompt long enough for the tcgen05 kernels, then decode steps on the streaming kernels."""
+    small): a prompt long enough for the tcgen05 kernels, then decode steps on the streaming kernels; in
+    float32 the same through the general kernels."""
     import tempfile
 
     import fieldrun_b200 as fr
     with tempfile.TemporaryDirectory() as folder:
         fr.write_random_model(folder, M2_SHAPED, fr.RandomInit(seed=4, matrix_std=0.02, norm_std=0.1, bias_std=0.01))
         config, weights = pm.read_model_folder(folder)
-        lm = fr.load(folder, dtype="bfloat16", max_tokens=512)
+        lm = fr.load(folder, dtype=dtype, max_tokens=512)
         ids = np.random.default_rng(11).integers(0, 2003, size=76).tolist()
         requests = {"r": ids, "s": ids[5:30]}
         steps = [[("r", 0, 70), ("s", 0, 20)]] + [[("r", 70 + k, 71 + k)] + ([("s", 20 + k, 21 + k)] if k < 5 else []) for k in range(6)]
@@ -245,9 +247,9 @@ def test_a_layer_of_minimax_m2_size():
             routes = recorder.of(key, len(tokens))
             hidden, margins, own = pm.hidden_states(config, weights, tokens, forced_routes=routes, return_routes=True)
             ref = hidden @ weights["lm_head.weight"].astype(np.float64).T
-            assert_close(logits[key], ref, "bfloat16", f"MiniMax-M2-sized layer, request {key}")
+            assert_close(logits[key], ref, dtype, f"MiniMax-M2-sized layer, request {key}")
             differs = (np.sort(own, axis=-1) != np.sort(routes, axis=-1)).any(axis=-1)
-            assert not (differs & (margins > 5e-3)).any()
+            assert not (differs & (margins > (5e-3 if dtype == "bfloat16" else 1e-5))).any()
 
 
 def test_a_step_whose_buffers_pass_two_to_the_31_elements():
