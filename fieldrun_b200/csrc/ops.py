@@ -33,7 +33,7 @@ _SIGNATURES = {
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifii",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
-    "frb_attention_decode_tma": "pppipipppppiiiifiip",
+    "frb_attention_decode_tma": "pppipipppppiiiifiiip",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
@@ -327,18 +327,30 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           head_dim, float(scale), int(window or 0), max_chunks)
 
 
+def decode_chunks_per_block(num_seqs: int, num_kv_heads: int, max_chunks: int, sms: int = 148) -> int:
+    """How many chunks of 256 keys one block of :func:`attention_decode_tma` takes: as many as still leave about
+    one block per SM (measured on a B200: a block's set-up and its combine cost about as much as three pages,
+    so long runs win as soon as the SMs have a block each: 32 sequences of 4,096 keys 4.7 TB/s with one chunk
+    per block, 5.8 with eight or more; 8 sequences of 32,768 keys 4.1 and 6.5)."""
+    return max(1, min(max_chunks, (num_seqs * num_kv_heads * max_chunks) // sms))
+
+
 def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                          seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                          out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                         window: Optional[int], max_chunks: int) -> None:
+                         window: Optional[int], max_chunks: int, chunks_per_block: Optional[int] = None) -> None:
     """As :func:`attention_decode_mma` for head sizes 64 and 128, with the pages copied into shared memory by
-    TMA (all pages of a block at once), which keeps far more bytes in flight."""
+    TMA through a ring of stages, which keeps far more bytes in flight; a block takes ``chunks_per_block``
+    chunks (default: :func:`decode_chunks_per_block`)."""
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want(part_o, torch.float32, "partial outputs")
+    if chunks_per_block is None:
+        chunks_per_block = decode_chunks_per_block(q.shape[0], num_kv_heads, max_chunks)
     _call("frb_attention_decode_tma", _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads,
-          num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)))
+          num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, int(chunks_per_block),
+          _ptr(tc_status(q.device)))
 
 
 def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,

@@ -381,12 +381,46 @@ def test_one_token_attention_on_tensor_cores(heads, kv_heads, head_dim, window, 
                            num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
                            max_chunks=chunks)
     ops().tc_status_check(q.device)
+    if kernel == "attention_decode_tma":          # blocks of several chunks give the same result up to rounding
+        for per_block in (2, 3, 8):
+            again = torch.full_like(q, 7.0)
+            ops().attention_decode_tma(q, keys, values, dev(table), dev(positions), dev(slot_of), part_o, part_ml, again,
+                                       num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window,
+                                       max_chunks=chunks, chunks_per_block=per_block)
+            ops().tc_status_check(q.device)
+            close(f64(again), f64(out), 1e-2, f"{per_block} chunks per block")
     ref = reference_attention(f64(q), kc, vc, table, positions, slot_of, heads, kv_heads, head_dim, scale, window)
     close(f64(out), ref, 1e-2, "one-token attention")
     general = torch.empty_like(q)
     ops().attention_generic(q, keys, values, dev(table), dev(positions), dev(slot_of), general, num_heads=heads,
                             num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
     close(f64(out), f64(general), 1e-2, "against the general kernel")
+
+
+def test_one_token_attention_with_every_sm_busy():
+    """32 sequences of 4,096 keys: two blocks on every SM for several rounds, copies that take their time.  A ring
+    of stages whose waits were right only while the copies were quick gave wrong results here and nowhere else."""
+    heads, kv_heads, head_dim, batch, context = 48, 8, 128, 32, 4096
+    pages_per = context // 64
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    keys = (torch.randn(batch * pages_per, kv_heads, 64, head_dim, device=DEV, generator=gen) * 0.3).to(torch.bfloat16)
+    values = (torch.randn(batch * pages_per, kv_heads, head_dim, 64, device=DEV, generator=gen) * 0.3).to(torch.bfloat16)
+    table = torch.arange(batch * pages_per, dtype=torch.int32, device=DEV).view(batch, pages_per).contiguous()
+    slots = torch.arange(batch, dtype=torch.int32, device=DEV)
+    q = torch.randn(batch, heads * head_dim, device=DEV, generator=gen).to(torch.bfloat16)
+    positions = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    chunks = context // 256
+    part_o = torch.empty(batch, heads, chunks, head_dim, dtype=torch.float32, device=DEV)
+    part_ml = torch.empty(batch, heads, chunks, 2, dtype=torch.float32, device=DEV)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=head_dim ** -0.5, window=None, max_chunks=chunks)
+    ref = torch.empty_like(q)
+    ops().attention_decode_mma(q, keys, values, table, positions, slots, part_o, part_ml, ref, **args)
+    for per_block in (None, 1, 2, 3, 8):
+        for _ in range(3):
+            out = torch.zeros_like(q)
+            ops().attention_decode_tma(q, keys, values, table, positions, slots, part_o, part_ml, out, chunks_per_block=per_block, **args)
+            ops().tc_status_check(q.device)
+            close(f64(out), f64(ref), 1e-2, f"{per_block} chunks per block against the kernel that loads into registers")
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 1, 128, None), (4, 4, 64, None), (20, 2, 32, 40),
