@@ -328,11 +328,16 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
 
 
 def decode_chunks_per_block(num_seqs: int, num_kv_heads: int, max_chunks: int, sms: int = 148) -> int:
-    """How many chunks of 256 keys one block of :func:`attention_decode_tma` takes: as many as still leave about
-    one block per SM (measured on a B200: a block's set-up and its combine cost about as much as three pages,
-    so long runs win as soon as the SMs have a block each: 32 sequences of 4,096 keys 4.7 TB/s with one chunk
-    per block, 5.8 with eight or more; 8 sequences of 32,768 keys 4.1 and 6.5)."""
-    return max(1, min(max_chunks, (num_seqs * num_kv_heads * max_chunks) // sms))
+    """How many chunks of 256 keys one block of :func:`attention_decode_tma` takes.  A block's set-up and its
+    combine cost about as much as three pages, so runs of several chunks win as soon as the SMs have a block
+    each (measured on a B200: 32 sequences of 4,096 keys 4.7 TB/s with one chunk per block, 5.85 with eight;
+    8 sequences of 32,768 keys 4.1 and 6.2).  Not more than eight: the grid is laid out for the longest
+    sequence of the step, and with longer runs a step of unequal sequences is left with a few long blocks.
+    The run is then shortened as far as the number of blocks per sequence stays the same (9 chunks: 5 + 4,
+    not 8 + 1)."""
+    most = max(1, min(8, max_chunks, (num_seqs * num_kv_heads * max_chunks) // sms))
+    blocks = -(-max_chunks // most)
+    return -(-max_chunks // blocks)
 
 
 def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
