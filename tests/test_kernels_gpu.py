@@ -745,3 +745,55 @@ def test_tcgen05_attention_finds_one_far_key_and_follows_a_late_maximum():
     positions, slot_of = np.arange(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
     ref = reference_attention(f64(q), f64(keys), f64(values), table, positions, slot_of, heads, kv_heads, head_dim, 1.0, None)
     close(f64(out), ref, 1.5e-2, "tcgen05 attention with a rising maximum")
+
+
+def test_tensor_core_attention_on_random_shapes():
+    """Random head counts and groups, lengths, starts, windows and page orders: the TMA-fed one-token kernel (with
+    blocks of one, of several and of the default number of chunks) and the tcgen05 prompt kernel against the
+    general kernel."""
+    rng = np.random.default_rng(7)
+    i32 = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
+    for trial in range(24):
+        head_dim = int(rng.choice([64, 128]))
+        kv_heads = int(rng.choice([1, 2, 8]))
+        heads = kv_heads * int(rng.choice([1, 4, 6, 16]))
+        batch = int(rng.choice([1, 3, 8, 20]))
+        scale = head_dim ** -0.5
+        window = None if rng.random() < 0.6 else int(rng.integers(1, 600))
+        prompt = trial % 2 == 1
+        if prompt:
+            q_lens = rng.integers(1, 500, size=batch)
+            starts = rng.integers(0, 300, size=batch) * (rng.random(size=batch) < 0.5)
+        else:
+            q_lens = np.ones(batch, dtype=np.int64)
+            starts = rng.integers(0, int(rng.choice([70, 300, 1500, 5000])), size=batch)
+        pages_per = (int((starts + q_lens).max()) + 63) // 64
+        total = batch * pages_per
+        keys = (torch.randn(total, kv_heads, 64, head_dim, device=DEV) * 0.5).to(torch.bfloat16)
+        values = (torch.randn(total, kv_heads, head_dim, 64, device=DEV) * 0.5).to(torch.bfloat16)
+        table = i32(rng.permutation(total)).view(batch, pages_per).contiguous()
+        rows = int(q_lens.sum())
+        q = torch.randn(rows, heads * head_dim, device=DEV).to(torch.bfloat16)
+        tok_pos = np.concatenate([starts[b] + np.arange(q_lens[b]) for b in range(batch)])
+        tok_slot = np.concatenate([np.full(q_lens[b], b) for b in range(batch)])
+        general = torch.empty_like(q)
+        common = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+        ops().attention_generic(q, keys, values, table, i32(tok_pos), i32(tok_slot), general, **common)
+        what = f"trial {trial}: {heads} heads over {kv_heads}, head size {head_dim}, window {window}, lengths {list(starts + q_lens)}"
+        if prompt:
+            tiles = [(b, q0) for b in range(batch) for q0 in range(0, int(q_lens[b]), 128)]
+            out = torch.full_like(q, 9.0)
+            ops().attention_prefill_tc(q, keys, values, table, i32([t[0] for t in tiles]), i32([t[1] for t in tiles]), i32(np.arange(batch)),
+                                       i32(starts), i32(q_lens), i32(np.concatenate([[0], np.cumsum(q_lens)])), out, **common)
+            ops().tc_status_check(q.device)
+            close(f64(out), f64(general), 1.5e-2, what)
+        else:
+            chunks = (int(starts.max()) + 1 + 255) // 256
+            part_o = torch.empty(batch, heads, chunks, head_dim, dtype=torch.float32, device=DEV)
+            part_ml = torch.empty(batch, heads, chunks, 2, dtype=torch.float32, device=DEV)
+            for per_block in (None, 1, int(rng.integers(2, 12))):
+                out = torch.full_like(q, 9.0)
+                ops().attention_decode_tma(q, keys, values, table, i32(starts), i32(np.arange(batch)), part_o, part_ml, out,
+                                           max_chunks=chunks, chunks_per_block=per_block, **common)
+                ops().tc_status_check(q.device)
+                close(f64(out), f64(general), 1.5e-2, f"{what}, {per_block} chunks per block")
