@@ -7,7 +7,7 @@ next-token top-1 over ``--n-eval`` positions (default 500) with a sliding contex
 and ``--dump`` writes the predictions one id per line (src/main.rs:3933-3941,
 4096-4104).  Here ``--model`` names a model folder (``--bundle`` is accepted for
 it), and ``--temperature``, ``--seed``, ``--eos``, ``--dtype`` and ``--prompts`` are
-what a batch engine with sampling adds.  ``random`` writes a model folder with
+what a batch engine with sampling adds; ``--device cpu`` and ``--kv-int8`` are recognised and refused with a reason.  ``random`` writes a model folder with
 random weights, the counterpart of the reference's offline ``convert`` step.
 
     python -m fieldrun_b200 --model DIR --ids ids.json --ctx 64 --generate 32
@@ -82,7 +82,14 @@ def _main(argv: list[str] | None = None) -> int:
     parser.add_argument("--seed", type=int, default=0, help="seed of temperature sampling")
     parser.add_argument("--eos", default=None, help="stop token ids, comma separated (default: the config's; 'none')")
     parser.add_argument("--batch", type=int, default=64, help="most sequences in one batch")
+    parser.add_argument("--device", default="auto", choices=["auto", "gpu", "cpu"],
+                        help="the reference's switch (src/main.rs:4036-4094); this library runs on the GPU only")
+    parser.add_argument("--kv-int8", action="store_true", help="the reference's 8-bit cache; not part of this library")
     args = parser.parse_args(argv)
+    if args.device == "cpu":
+        raise SystemExit("[fieldrun_b200] --device cpu: this library has no CPU path; it runs on one CUDA device (sm_100a)")
+    if args.kv_int8:
+        raise SystemExit("[fieldrun_b200] --kv-int8: quantized caches are not part of this library; the cache holds the model's dtype")
 
     import fieldrun_b200 as fr
 

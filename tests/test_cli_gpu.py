@@ -58,3 +58,7 @@ def test_errors_are_one_line_messages(tmp_path):
     proc = subprocess.run([sys.executable, "-m", "fieldrun_b200", "--model", str(tmp_path / "nothing"), "--ids", "x.json"],
                           cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 1 and proc.stderr.startswith("[fieldrun_b200] error:") and "Traceback" not in proc.stderr
+    for flag, word in ((["--device", "cpu"], "no CPU path"), (["--kv-int8"], "quantized caches")):
+        proc = subprocess.run([sys.executable, "-m", "fieldrun_b200", "--model", str(tmp_path / "nothing"), "--ids", "x.json", *flag],
+                              cwd=ROOT, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 1 and word in proc.stderr and "Traceback" not in proc.stderr
