@@ -177,6 +177,7 @@ def main() -> int:
             tokens = device_step(slots, tokens)
         stop.record()
         torch.cuda.synchronize()
+        ops.tc_status_check(engine.device)               # no kernel of the timed steps gave up on a wait
         return start.elapsed_time(stop) / steps, ops.launches() - before, tokens
 
     def decode_bytes(slots):

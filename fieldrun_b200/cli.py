@@ -85,6 +85,8 @@ def _main(argv: list[str] | None = None) -> int:
     parser.add_argument("--device", default="auto", choices=["auto", "gpu", "cpu"],
                         help="the reference's switch (src/main.rs:4036-4094); this library runs on the GPU only")
     parser.add_argument("--kv-int8", action="store_true", help="the reference's 8-bit cache; not part of this library")
+    parser.add_argument("--profile", action="store_true",
+                        help="time every kernel with CUDA events (steps run directly, slower) and print the sums as JSON lines")
     args = parser.parse_args(argv)
     if args.device == "cpu":
         raise SystemExit("[fieldrun_b200] --device cpu: this library has no CPU path; it runs on one CUDA device (sm_100a)")
@@ -118,10 +120,20 @@ def _main(argv: list[str] | None = None) -> int:
             eos = []
         else:
             eos = [int(t) for t in args.eos.split(",") if t]
+        if args.profile:
+            from .csrc import ops
+            lm.engine.record_steps = False                   # a replayed step is one launch: nothing to tell apart
+            ops.timing_start()
         started = time.perf_counter()
         outputs = lm.generate_batch(prompts, args.generate, eos=eos, temperature=args.temperature, seed=args.seed,
                                     ignore_eos=(eos == []))
         seconds = time.perf_counter() - started
+        if args.profile:
+            report = ops.timing_report()
+            total = sum(ms for _, ms in report.values()) or 1.0
+            for name, (launches, ms) in sorted(report.items(), key=lambda item: -item[1][1]):
+                print(json.dumps({"kernel": name, "launches": launches, "ms": round(ms, 3), "share": round(ms / total, 4)}),
+                      file=sys.stderr)
         total = sum(len(o) for o in outputs)
         for prompt, output in zip(prompts, outputs):
             print(f"[fieldrun_b200] generate {len(output)} tokens from a {len(prompt)}-token prompt")

@@ -426,17 +426,21 @@ def tc_status(device) -> torch.Tensor:
 
 
 def tc_status_check(device) -> None:
-    """Raise if a tensor-core expert kernel reported a wait that gave up since the last check (this reads
-    one int from the device, so it waits for the work before it)."""
+    """Raise if a kernel reported a wait that gave up since the last check (this reads one int from the
+    device, so it waits for the work before it)."""
     key = str(device)
     if key in _TC_STATUS:
-        code = int(_TC_STATUS[key].item())
-        if code != 0:
-            _TC_STATUS[key].zero_()
-            where = {1: "the producer waiting for a free stage", 2: "the MMA thread waiting for a loaded stage",
-                     3: "the epilogue waiting for the accumulators",
-                     4: "one-token attention waiting for a page's copy"}.get(code, f"code {code}")
-            raise KernelError(f"a tensor-core kernel's wait gave up ({where}); the step's results are not valid")
+        tc_status_raise(device, int(_TC_STATUS[key].item()))
+
+
+def tc_status_raise(device, code: int) -> None:
+    """Raise for a status word that was read from the device (0: nothing happened) and clear the word."""
+    if code != 0:
+        _TC_STATUS[str(device)].zero_()
+        where = {1: "the producer waiting for a free stage", 2: "the MMA thread waiting for a loaded stage",
+                 3: "the epilogue waiting for the accumulators",
+                 4: "one-token attention waiting for a page's copy"}.get(code, f"code {code}")
+        raise KernelError(f"a tensor-core kernel's wait gave up ({where}); the step's results are not valid")
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

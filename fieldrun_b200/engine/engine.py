@@ -221,12 +221,16 @@ class Engine:
         """One token per row of logits: the largest logit where the temperature is 0, else a sample with the
         row's uniform number."""
         rows = logits.shape[0]
-        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        # one more int: the kernels' status word comes to the host in the same copy as the tokens
+        out = torch.empty(rows + 1, dtype=torch.int32, device=logits.device)
         temp_dev = uni_dev = None
         if temperatures is not None and any(t > 0 for t in temperatures):
             if uniforms is None or len(uniforms) != rows or len(temperatures) != rows:
                 raise StepError("sampling needs one temperature and one uniform number per row")
             both = torch.tensor([list(temperatures), list(uniforms)], dtype=torch.float32).to(logits.device)
             temp_dev, uni_dev = both[0], both[1]
-        ops.sample_rows(logits.contiguous(), temp_dev, uni_dev, out)
-        return out.tolist()
+        ops.sample_rows(logits.contiguous(), temp_dev, uni_dev, out[:rows])
+        out[rows:].copy_(ops.tc_status(self.device))
+        picked = out.tolist()
+        ops.tc_status_raise(self.device, picked.pop())     # a kernel that gave up on a wait must not pass for a result
+        return picked

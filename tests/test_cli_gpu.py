@@ -53,6 +53,12 @@ def test_random_generate_score_and_dump(tmp_path):
     tokens = lambda text: [line for line in text.splitlines() if line and line[0].isdigit()]
     assert tokens(first) == tokens(again) and len(tokens(first)) == 3
 
+    proc = subprocess.run([sys.executable, "-m", "fieldrun_b200", "--model", folder, "--ids", str(ids_path), "--ctx", "12",
+                           "--generate", "4", "--eos", "none", "--profile"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    kernels = [json.loads(line) for line in proc.stderr.splitlines() if line.startswith("{")]
+    assert any(k["kernel"] == "rmsnorm" and k["launches"] > 0 for k in kernels) and abs(sum(k["share"] for k in kernels) - 1) < 0.01
+
 
 def test_errors_are_one_line_messages(tmp_path):
     proc = subprocess.run([sys.executable, "-m", "fieldrun_b200", "--model", str(tmp_path / "nothing"), "--ids", "x.json"],
