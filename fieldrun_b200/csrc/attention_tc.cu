@@ -14,107 +14,25 @@
 //
 // Every wait on an mbarrier gives up after about a second (at once when another wait of the block has given
 // up), sets `status`, and the block leaves through the common exit, which frees the tensor memory.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define AT_QUERIES 128
 #define AT_THREADS 192         // warp 0: TMA producer, warp 1: MMA issuer and tensor-memory owner, warps 2-5: softmax
 #define AT_STAGES 3
 #define AT_STEP_PAGES 2        // cache pages per step of the inner loop
 #define AT_STEP_KEYS (AT_STEP_PAGES * FRB_PAGE)
-#define AT_WAIT_CYCLES (2000000000ll)
 #define AT_RAISE 8.0f          // the running maximum follows a page's maximum only beyond this margin
 
+using namespace frb_tma;
+using namespace frb_tc;
+
 namespace {
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void bar_expect(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
-// false when the phase did not complete in time, or another wait of this block already gave up
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
-    const uint32_t addr = smem_addr(bar);
-    const long long start = clock64();
-    for (;;) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if (*failed || clock64() - start > AT_WAIT_CYCLES) { *failed = 1; return false; }
-    }
-}
-
-__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// K-major operand tile in shared memory: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-// A from tensor memory
-__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 
 // 2^x by the special-function unit (relative error about 2^-22; -inf and anything below -126 give 0)
 __device__ __forceinline__ float exp2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
 }
 
 }  // namespace
@@ -172,15 +90,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < AT_STAGES; ++s) { bar_init(&kv_full[s], 1); bar_init(&kv_empty[s], 1); }
         for (int i = 0; i < 2; ++i) { bar_init(&s_full[i], 1); bar_init(&s_free[i], 4); bar_init(&p_full[i], 4); bar_init(&pv_done[i], 1); }
         failed_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        bar_init_fence();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+        tmem_alloc(&tmem_slot, TMEM_COLS);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem = tmem_slot;
 
     if (warp == 0) {
@@ -188,7 +105,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             bar_expect(&q_full, Q_BYTES);
 #pragma unroll
             for (int kb = 0; kb < KBLOCKS; ++kb)
-                tma_2d(q_tile + kb * (AT_QUERIES * 128), &map_q, head * HD + kb * 64, tok0, &q_full);
+                load_2d(q_tile + kb * (AT_QUERIES * 128), &map_q, head * HD + kb * 64, tok0, &q_full);
             for (int j = 0; j < num_steps; ++j) {
                 const int s = j % AT_STAGES;
                 if (!bar_wait(&kv_empty[s], ((j / AT_STAGES) & 1) ^ 1, failed)) { atomicExch(p.status, 11); break; }
@@ -200,8 +117,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const int row = page * p.num_kv_heads + kvh;
 #pragma unroll
                     for (int kb = 0; kb < KBLOCKS; ++kb)
-                        tma_2d(dst + kb * K_BLOCK_BYTES + h * (FRB_PAGE * 128), &map_k, kb * 64, row * FRB_PAGE, &kv_full[s]);
-                    tma_2d(dst + AT_STEP_PAGES * K_BYTES + h * V_BYTES, &map_v, 0, row * HD, &kv_full[s]);
+                        load_2d(dst + kb * K_BLOCK_BYTES + h * (FRB_PAGE * 128), &map_k, kb * 64, row * FRB_PAGE, &kv_full[s]);
+                    load_2d(dst + AT_STEP_PAGES * K_BYTES + h * V_BYTES, &map_v, 0, row * HD, &kv_full[s]);
                 }
             }
         }
@@ -211,8 +128,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // An MMA of 16 along the inner size takes the tensor core about 130 cycles whatever N up to 128 (clock
             // stamps around the issue; a second issuing thread changes nothing): a step of two pages asks for half
             // as many of them per key as a step of one.
-            const uint32_t idesc_common = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_QUERIES >> 4) << 24);
-            const uint32_t idesc_o = idesc_common | ((uint32_t)(HD >> 3) << 17);
+            const uint32_t idesc_o = instr_desc_bf16(AT_QUERIES, HD);
             const uint64_t q_desc = tile_desc(smem_addr(q_tile));
             bool ok = bar_wait(&q_full, 0, failed);
             if (!ok) atomicExch(p.status, 12);
@@ -221,9 +137,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int s = j % AT_STAGES;
                 if (!bar_wait(&kv_full[s], (j / AT_STAGES) & 1, failed)) { atomicExch(p.status, 13); return false; }
                 if (j >= 2 && !bar_wait(&s_free[j & 1], ((j - 2) >> 1) & 1, failed)) { atomicExch(p.status, 14); return false; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
-                const uint32_t idesc_s = idesc_common | ((uint32_t)((pages * FRB_PAGE) >> 3) << 17);
+                const uint32_t idesc_s = instr_desc_bf16(AT_QUERIES, pages * FRB_PAGE);
                 const uint64_t k_desc = tile_desc(smem_addr(stage0 + (size_t)s * STAGE_BYTES));
 #pragma unroll
                 for (int kb = 0; kb < KBLOCKS; ++kb)
@@ -239,7 +155,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (j + 1 < num_steps) ok = issue_scores(j + 1);
                 if (!ok) break;
                 if (!bar_wait(&p_full[j & 1], (j >> 1) & 1, failed)) { atomicExch(p.status, 15); ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
                 const int s = j % AT_STAGES;
                 const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
                 const uint64_t v_desc = tile_desc(smem_addr(stage0 + (size_t)s * STAGE_BYTES + AT_STEP_PAGES * K_BYTES));
@@ -263,7 +179,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool ok = true;
         for (int j = 0; j < num_steps && ok; ++j) {
             if (!bar_wait(&s_full[j & 1], (j >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 16); ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const int pages = min(AT_STEP_PAGES, num_pages - AT_STEP_PAGES * j);
             const int key0 = (first_page + AT_STEP_PAGES * j) * FRB_PAGE;
             const int num_keys = pages * FRB_PAGE;
@@ -271,8 +187,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < AT_STEP_KEYS / 16; ++c)
                 if (16 * c < num_keys) tmem_ld16(lane_base + S_COL0 + AT_STEP_KEYS * (j & 1) + 16 * c, raw[c]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            tmem_wait_ld();
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) bar_arrive(&s_free[j & 1]);
             // Most steps lie wholly before the tile's first query (and inside the window): no key of theirs is
@@ -314,18 +230,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const float bb = exp2_fast(fmaf(__uint_as_float(raw[c][i + 1]), p.scale2, -m_sub));
                     sums[0] += a;
                     sums[1] += bb;
-                    packed[c >> 1][(c & 1) * 8 + (i >> 1)] = pack2(a, bb);
+                    packed[c >> 1][(c & 1) * 8 + (i >> 1)] = pack_bf16x2(a, bb);
                 }
             l_sum = l_sum * corr + (sums[0] + sums[1]);
             if (j >= 2 && !bar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 17); ok = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, raise)) {     // rare: O must follow the new maximum
                 if (!bar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 18); ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fence_after_sync();
 #pragma unroll 1
                 for (int c = 0; c < HD / 16; ++c) {
                     uint32_t o[16];
                     tmem_ld16(lane_base + O_COL + 16 * c, o);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
                     tmem_st16(lane_base + O_COL + 16 * c, o);
@@ -334,8 +250,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < AT_STEP_KEYS / 32; ++c)
                 if (32 * c < num_keys) tmem_st16(lane_base + P_COL0 + (AT_STEP_KEYS / 2) * (j & 1) + 16 * c, packed[c]);
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            tmem_wait_st();
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) bar_arrive(&p_full[j & 1]);
         }
@@ -344,31 +260,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!bar_wait(&pv_done[last & 1], (last >> 1) & 1, failed)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
         }
         if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fence_after_sync();
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
             bf16* dst = p.out + ((size_t)(tok0 + row) * p.num_heads + head) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 16; ++c) {
                 uint32_t o[16];
                 tmem_ld16(lane_base + O_COL + 16 * c, o);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tmem_wait_ld();
                 if (valid) {
                     uint4 lo4, hi4;
-                    lo4.x = pack2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-                    lo4.y = pack2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-                    lo4.z = pack2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-                    lo4.w = pack2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-                    hi4.x = pack2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-                    hi4.y = pack2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-                    hi4.z = pack2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-                    hi4.w = pack2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                    lo4.x = pack_bf16x2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+                    lo4.y = pack_bf16x2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+                    lo4.z = pack_bf16x2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+                    lo4.w = pack_bf16x2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+                    hi4.x = pack_bf16x2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+                    hi4.y = pack_bf16x2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                    hi4.z = pack_bf16x2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                    hi4.w = pack_bf16x2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
                     reinterpret_cast<uint4*>(dst + 16 * c)[0] = lo4;
                     reinterpret_cast<uint4*>(dst + 16 * c)[1] = hi4;
                 }
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (failed_flag && warp == 0 && lane == 0) {
         // copies may still be on their way into this block's shared memory: give them a bounded time to land
@@ -377,39 +293,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < AT_STAGES; ++s) { zero = 0; bar_wait(&kv_full[s], 0, &zero); }
     }
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    if (warp == 1) tmem_free(tmem, TMEM_COLS);
 }
 
 // ----------------------------------------------------------------------------- host side
-
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeFn encoder() {
-    static EncodeFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeFn)ptr;
-    }
-    return fn;
-}
-
-// row-major bf16 [rows, cols]; boxes of [box_rows, 64 columns], 128-byte swizzle, zeros outside
-static bool map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    EncodeFn fn = encoder();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {64, box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 // q bf16 [num_tokens, nh, hd]; k_pages [pages, nkv, 64, hd]; v_pages [pages, nkv, hd, 64]; tiles of 128 queries.
 // status: one int on the device, zero before the call.
@@ -425,9 +312,9 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
                   num_heads, num_kv_heads);
     CUtensorMap map_q, map_k, map_v;
     const uint64_t kv_rows = (uint64_t)num_pages * num_kv_heads;
-    FRB_CHECK_ARG(map_2d(&map_q, q, num_tokens, (uint64_t)num_heads * head_dim, AT_QUERIES) &&
-                  map_2d(&map_k, k_pages, kv_rows * FRB_PAGE, head_dim, FRB_PAGE) &&
-                  map_2d(&map_v, v_pages, kv_rows * head_dim, FRB_PAGE, head_dim),
+    FRB_CHECK_ARG(map_rows_of_64(&map_q, q, num_tokens, (uint64_t)num_heads * head_dim, AT_QUERIES) &&
+                  map_rows_of_64(&map_k, k_pages, kv_rows * FRB_PAGE, head_dim, FRB_PAGE) &&
+                  map_rows_of_64(&map_v, v_pages, kv_rows * head_dim, FRB_PAGE, head_dim),
                   "tensor-core attention: cuTensorMapEncodeTiled failed or is not available");
     AttnTcParams p;
     p.page_table = page_table; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start;

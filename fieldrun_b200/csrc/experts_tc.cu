@@ -12,91 +12,14 @@
 //
 // Every wait on an mbarrier gives up after about a second, records a code in `status` and lets
 // the block leave through the common exit, which frees the tensor memory; the host checks `status`.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define TC_FEATS 128          // features per block: M of the MMA
 #define TC_KBLOCK 64          // k per stage: 64 bf16 = one 128-byte swizzle row
 #define TC_THREADS 192        // warp 0: TMA producer, warp 1: MMA issuer and tensor-memory owner, warps 2-5: epilogue
-#define TC_WAIT_CYCLES (2000000000ll)   // about a second: a wait that lasts this long gives up
 
-namespace {
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Polls until the phase with the given parity has completed; false if it did not within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    const long long start = clock64();
-    for (;;) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if (clock64() - start > TC_WAIT_CYCLES) return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-// Shared-memory operand descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle; groups of 8 rows
-// lie 1024 bytes apart (stride byte offset); descriptor version 1 of this architecture.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
-    desc |= (uint64_t)1 << 16;                                // leading byte offset (not used by swizzled K-major)
-    desc |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset
-    desc |= (uint64_t)1 << 46;                                // version
-    desc |= (uint64_t)2 << 61;                                // 128-byte swizzle
-    return desc;
-}
-
-// D[tmem] (+)= A[smem] * B[smem]^T, one thread issues.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-}  // namespace
+using namespace frb_tma;
+using namespace frb_tc;
 
 struct TcParams {
     const int* tile_expert;
@@ -133,121 +56,91 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     uint8_t* stage_base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);      // swizzled tiles: 1024-byte aligned
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&done_bar, 1);
+        for (int s = 0; s < p.stages; ++s) { bar_init(&full_bar[s], 1); bar_init(&empty_bar[s], 1); }
+        bar_init(&done_bar, 1);
         failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        bar_init_fence();
     }
     if (warp == 1) {                                            // one warp allocates the accumulators' columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"((uint32_t)p.tmem_cols));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+        tmem_alloc(&tmem_base_slot, (uint32_t)p.tmem_cols);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const int s = kb % p.stages;
-                if (!mbar_wait(&empty_bar[s], ((kb / p.stages) & 1) ^ 1)) { failed = 1; atomicExch(p.status, 1); break; }
+                if (!bar_wait(&empty_bar[s], ((kb / p.stages) & 1) ^ 1, &failed)) { atomicExch(p.status, 1); break; }
                 uint8_t* dst = stage_base + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], stage_bytes);
-                tma_load_2d(dst, &map_w, kb * TC_KBLOCK, w_row_gate, &full_bar[s]);
-                if (PAIRED) tma_load_2d(dst + w_bytes, &map_w, kb * TC_KBLOCK, w_row_up, &full_bar[s]);
-                tma_load_2d(dst + w_bytes * (PAIRED ? 2 : 1), &map_x, kb * TC_KBLOCK, row0, &full_bar[s]);
+                bar_expect(&full_bar[s], stage_bytes);
+                load_2d(dst, &map_w, kb * TC_KBLOCK, w_row_gate, &full_bar[s]);
+                if (PAIRED) load_2d(dst + w_bytes, &map_w, kb * TC_KBLOCK, w_row_up, &full_bar[s]);
+                load_2d(dst + w_bytes * (PAIRED ? 2 : 1), &map_x, kb * TC_KBLOCK, row0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: float32 accumulate, bf16 x bf16, both K-major, N = NT, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(TC_FEATS >> 4) << 24);
+            const uint32_t idesc = instr_desc_bf16(TC_FEATS, p.NT);
             bool ok = true;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
                 const int s = kb % p.stages;
-                if (!mbar_wait(&full_bar[s], (kb / p.stages) & 1)) { failed = 1; atomicExch(p.status, 2); ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t base = smem_u32(stage_base + (size_t)s * stage_bytes);
+                if (!bar_wait(&full_bar[s], (kb / p.stages) & 1, &failed)) { atomicExch(p.status, 2); ok = false; break; }
+                fence_after_sync();
+                const uint32_t base = smem_addr(stage_base + (size_t)s * stage_bytes);
                 const uint32_t x_addr = base + w_bytes * (PAIRED ? 2 : 1);
 #pragma unroll
                 for (int k = 0; k < TC_KBLOCK / 16; ++k) {               // 16 k per MMA: 32 bytes along the swizzled row
-                    const uint64_t desc_x = operand_desc(x_addr + k * 32);
-                    umma_bf16(tmem_base, operand_desc(base + k * 32), desc_x, idesc, (kb | k) != 0);
-                    if (PAIRED) umma_bf16(tmem_base + p.NT, operand_desc(base + w_bytes + k * 32), desc_x, idesc, (kb | k) != 0);
+                    const uint64_t desc_x = tile_desc(x_addr + k * 32);
+                    mma_ss(tmem_base, tile_desc(base + k * 32), desc_x, idesc, (kb | k) != 0);
+                    if (PAIRED) mma_ss(tmem_base + p.NT, tile_desc(base + w_bytes + k * 32), desc_x, idesc, (kb | k) != 0);
                 }
-                umma_commit(&empty_bar[s]);                              // the stage is free once these MMAs have read it
+                mma_commit(&empty_bar[s]);                              // the stage is free once these MMAs have read it
             }
-            umma_commit(&done_bar);                                      // arrives when every MMA above has finished
+            mma_commit(&done_bar);                                      // arrives when every MMA above has finished
         }
     } else {
         const int quarter = warp & 3;                                    // the 32 lanes of tensor memory this warp may read
-        bool ok = mbar_wait(&done_bar, 0);
-        if (!ok && lane == 0) { failed = 1; atomicExch(p.status, 3); }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        bool ok = bar_wait(&done_bar, 0, &failed);
+        if (!ok && lane == 0) atomicExch(p.status, 3);
+        fence_after_sync();
         if (ok && !failed) {
             const int f = f0 + quarter * 32 + lane;
             OutT* out = (OutT*)p.out;
             for (int c0 = 0; c0 < p.NT && c0 < rows; c0 += 16) {
-                float gate[16], up[16];
+                uint32_t gate[16], up[16];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + c0;
-                tmem_load16(taddr, gate);
-                if (PAIRED) tmem_load16(taddr + p.NT, up);
+                tmem_ld16(taddr, gate);
+                if (PAIRED) tmem_ld16(taddr + p.NT, up);
+                tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int n = c0 + j;
                     if (n < rows) {
-                        float v = gate[j];
-                        if (PAIRED) v = v / (1.0f + expf(-v)) * up[j];
+                        float v = __uint_as_float(gate[j]);
+                        if (PAIRED) v = v / (1.0f + expf(-v)) * __uint_as_float(up[j]);
                         out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
                     }
                 }
             }
         }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_before_sync();
     __syncthreads();
     if (failed && warp == 0 && lane == 0) {
         // copies may still be on their way into this block's shared memory: give them a bounded time to land
-        for (int s = 0; s < p.stages; ++s) mbar_wait(&full_bar[s], 0);
+        for (int s = 0; s < p.stages; ++s) { int again = 0; bar_wait(&full_bar[s], 0, &again); }
     }
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols));
+        tmem_free(tmem_base, (uint32_t)p.tmem_cols);
     }
 }
 
 // ----------------------------------------------------------------------------- host side
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-// A map over a row-major bf16 matrix [rows, cols]; boxes of [box_rows, 64], 128-byte swizzle, zeros outside.
-static bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {TC_KBLOCK, box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 // W bf16 [E][(paired ? 2 : 1) F][K]; X bf16 [x_rows_total, K] with the rows of each expert together (sorted
 // order); tiles of tile_rows = 32, 64, 128 or 256 rows.  status: one int on the device, zero before the call.
@@ -262,7 +155,7 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
     FRB_CHECK_ARG(((uintptr_t)W & 15) == 0 && ((uintptr_t)X & 15) == 0, "expert tensor-core product: operands must be 16-byte aligned");
     CUtensorMap map_w, map_x;
     const uint64_t w_rows = (uint64_t)num_experts * (paired ? 2 : 1) * F;
-    FRB_CHECK_ARG(make_map(&map_w, W, w_rows, K, TC_FEATS) && make_map(&map_x, X, x_rows_total, K, tile_rows),
+    FRB_CHECK_ARG(map_rows_of_64(&map_w, W, w_rows, K, TC_FEATS) && map_rows_of_64(&map_x, X, x_rows_total, K, tile_rows),
                   "expert tensor-core product: cuTensorMapEncodeTiled failed or is not available");
     TcParams p;
     p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.num_tiles = num_tiles; p.offsets = offsets; p.out = out;
