@@ -392,7 +392,8 @@ def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: 
                      tile_rows: int, ids: torch.Tensor, weights: torch.Tensor, offsets: torch.Tensor,
                      sorted_token: torch.Tensor, row_of_assign: torch.Tensor, tile_expert: torch.Tensor,
                      tile_row0: torch.Tensor, num_tiles: torch.Tensor) -> None:
-    """Expert choice and expert-sorted lists in one launch, for steps of at most 1024 (token, expert) pairs."""
+    """Expert choice and expert-sorted lists in one launch by one block, for steps of at most 1024 (token, expert)
+    pairs; the parts use it up to ``SMALL_ROUTE_TOKENS`` tokens, beyond which the separate kernels are faster."""
     _want(logits, torch.float32, "router logits")
     tokens, experts = logits.shape
     _call("frb_route_plan_small", _ptr(logits), _ptr(bias), tokens, experts, top_k, int(renormalize), float(routed_scale),
@@ -471,7 +472,7 @@ def router_small(act32: torch.Tensor, router: torch.Tensor, logits: torch.Tensor
                  offsets: torch.Tensor, sorted_token: torch.Tensor, row_of_assign: torch.Tensor, tile_expert: torch.Tensor,
                  tile_row0: torch.Tensor, num_tiles: torch.Tensor) -> None:
     """Router logits (float32 rows x float32 weight), expert choice and expert-sorted lists in one launch, for
-    steps of at most 1024 (token, expert) pairs."""
+    steps of at most ``ROUTER_SMALL_TOKENS`` tokens (a decode step of a small batch)."""
     _want(act32, torch.float32, "router input")
     _want(router, torch.float32, "router weight")
     _want(logits, torch.float32, "router logits")
