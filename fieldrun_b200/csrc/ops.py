@@ -37,6 +37,7 @@ _SIGNATURES = {
     "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
+    "frb_router_logits": "ppiiip",
     "frb_expert_gemm_tc": "pipippppiipiiip",
     "frb_gather_rows_bf16": "pppii",
     "frb_attention_prefill_tc": "pippipippipppppiiifip",
@@ -386,6 +387,18 @@ def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Ten
 SMALL_ROUTE_ASSIGNMENTS = 1024
 SMALL_ROUTE_TOKENS = 16       # one token per warp of the one-block kernel: beyond that the separate kernels are faster
 ROUTER_SMALL_TOKENS = 8       # most tokens of a step for router_small
+
+
+ROUTER_LOGITS_TOKENS = 256     # up to this many tokens the router's float32 product is this library's kernel
+
+
+def router_logits(act32: torch.Tensor, router: torch.Tensor, logits: torch.Tensor) -> None:
+    """logits [T, E] = act32 [T, width] x router [E, width]^T in float32, for steps of a few hundred tokens at most
+    (each block re-reads its eight tokens' rows: beyond that the library's product is the better one)."""
+    _want(act32, torch.float32, "router input")
+    _want(router, torch.float32, "router weight")
+    _want(logits, torch.float32, "router logits")
+    _call("frb_router_logits", _ptr(act32), _ptr(router), act32.shape[1], act32.shape[0], router.shape[0], _ptr(logits))
 
 
 def route_plan_small(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,

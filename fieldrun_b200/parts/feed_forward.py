@@ -90,9 +90,19 @@ class RoutedExperts(FeedForward):
             self.w2[e].copy_(down)
 
     # -- one step --------------------------------------------------------------------------------------
+    def logits(self, ctx, act32: torch.Tensor) -> torch.Tensor:
+        """Router logits: float32 rows, float32 weight, no rounding.  Few rows: this library's kernel (the
+        library's float32 product is slow on a handful of rows); many: the library."""
+        tokens = act32.shape[0]
+        if tokens <= ops.ROUTER_LOGITS_TOKENS and self.hidden_size % 4 == 0:
+            out = ctx.buffer("experts.logits", (tokens, self.num_experts), torch.float32)
+            ops.router_logits(act32, self.router, out)
+            return out
+        return linear(act32, self.router)
+
     def route(self, ctx, act32: torch.Tensor):
         tokens = act32.shape[0]
-        logits = linear(act32, self.router)                       # float32 rows, float32 weight: no rounding
+        logits = self.logits(ctx, act32)
         ids = ctx.buffer("experts.ids", (tokens, self.top_k), torch.int32)
         weights = ctx.buffer("experts.weights", (tokens, self.top_k), torch.float32)
         ops.router_topk(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, ids, weights)
@@ -190,7 +200,7 @@ class RoutedExperts(FeedForward):
                              ids, weights, p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"],
                              p["tile_row0"], p["num_tiles"])
         else:
-            logits = linear(act32, self.router)
+            logits = self.logits(ctx, act32)
             ops.route_plan_small(logits, self.bias, self.top_k, self.renormalize, self.routed_scale, tile_rows, ids, weights,
                                  p["offsets"], p["sorted_token"], p["row_of_assign"], p["tile_expert"], p["tile_row0"],
                                  p["num_tiles"])

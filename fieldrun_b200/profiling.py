@@ -203,7 +203,7 @@ def small_kernels(launches: int, tokens: int) -> dict:
     return out
 
 
-def whole_step(kind: str, launches: int) -> dict:
+def whole_step(kind: str, launches: int, batch: int = 8) -> dict:
     """Two layers of MiniMax-M2's sizes stepped through the engine: ``step_decode`` runs `launches` decode steps
     of 8 sequences over 2,048-token contexts, ``step_prefill`` one prompt of 2,048 tokens `launches` times.  The
     measured steps lie between cudaProfilerStart and cudaProfilerStop, so that
@@ -213,7 +213,7 @@ def whole_step(kind: str, launches: int) -> dict:
               "num_attention_heads": HEADS, "num_key_value_heads": KV_HEADS, "head_dim": HEAD_DIM, "rotary_dim": 64,
               "rope_theta": 5e6, "use_qk_norm": True, "num_local_experts": 256, "num_experts_per_tok": 8,
               "intermediate_size": WIDTH, "vocab_size": 200064, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
-    batch, prompt = (8, 2048) if kind == "decode" else (1, 2048)
+    batch, prompt = (batch, 2048) if kind == "decode" else (1, 2048)
     lm = random_model(config, RandomInit(seed=2, bias_std=0.01), dtype="bfloat16", max_tokens=(batch + 1) * (prompt + 128),
                       num_slots=batch + 1)
     engine = lm.engine
@@ -223,7 +223,10 @@ def whole_step(kind: str, launches: int) -> dict:
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if kind == "decode":
         slots = [engine.new_sequence() for _ in range(batch)]
-        tokens = engine.pick(engine.step(slots, prompts(batch)))
+        tokens: list[int] = []
+        for first in range(0, batch, 8):                   # eight prompts to a step keep its buffers small
+            group = slots[first:first + 8]
+            tokens += engine.pick(engine.step(group, prompts(len(group))))
         for _ in range(3):
             tokens = engine.pick(engine.step(slots, [[t] for t in tokens]))
         torch.cuda.synchronize()
@@ -260,7 +263,7 @@ CASES = {
     "attention_prefill": lambda n: attention("prefill", n),
     "attention_prefill_tc": lambda n: attention("prefill_tc", n),
     "attention_prefill_tc_long": lambda n: attention("prefill_tc_long", n),
-    "step_decode": lambda n: whole_step("decode", n),
+    "step_decode": lambda n, batch=8: whole_step("decode", n, batch),
     "step_prefill": lambda n: whole_step("prefill", n),
     "decode_small_kernels": lambda n: small_kernels(n, 8),
     "prefill_small_kernels": lambda n: small_kernels(n, 2048),
@@ -271,12 +274,13 @@ def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("case", choices=sorted(CASES) + ["all"])
     parser.add_argument("--launches", type=int, default=5)
+    parser.add_argument("--batch", type=int, default=8, help="sequences of step_decode")
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("fieldrun_b200.profiling needs a CUDA device")
     torch.manual_seed(0)
     for name in ([c for c in sorted(CASES) if not c.startswith("step_")] if args.case == "all" else [args.case]):
-        print(json.dumps(CASES[name](args.launches)))
+        print(json.dumps(CASES[name](args.launches, args.batch) if name == "step_decode" else CASES[name](args.launches)))
     return 0
 
 

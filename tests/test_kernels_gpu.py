@@ -797,3 +797,13 @@ def test_tensor_core_attention_on_random_shapes():
                                            max_chunks=chunks, chunks_per_block=per_block, **common)
                 ops().tc_status_check(q.device)
                 close(f64(out), f64(general), 1.5e-2, f"{what}, {per_block} chunks per block")
+
+
+@pytest.mark.parametrize("tokens,experts,width", [(1, 6, 72), (9, 256, 3072), (64, 256, 3072), (200, 10, 100)])
+def test_router_logits_in_float32(tokens, experts, width):
+    rng = np.random.default_rng(30)
+    act = rng.normal(size=(tokens, width)).astype(np.float32)
+    router = (rng.normal(size=(experts, width)) * 0.05).astype(np.float32)
+    logits = torch.full((tokens, experts), 7.0, dtype=torch.float32, device=DEV)
+    ops().router_logits(dev(act), dev(router), logits)
+    close(f64(logits), act.astype(np.float64) @ router.astype(np.float64).T, 2e-6, "router logits")
