@@ -25,6 +25,7 @@ from .config.registry import Architecture, architecture_for
 from .engine.engine import Engine
 from .engine.generate import Generated, Request, generate as run_requests
 from .engine.model import DecoderModel, parse_dtype
+from .sampling import SamplingParams
 from .weights import FolderSource, MemorySource, RandomInit, write_model_folder
 
 
@@ -78,11 +79,14 @@ class LanguageModel:
     def generate_batch(self, prompts: Sequence[Sequence[int]], max_tokens: int, *, eos: Optional[Sequence[int]] = None,
                        temperature: float = 0.0, seed: int = 0, ignore_eos: bool = False,
                        emit: Optional[Callable[[int, int], Optional[bool]]] = None,
-                       return_reasons: bool = False):
-        """Generate for many prompts of unequal lengths; ``eos`` defaults to the configuration's stop tokens."""
+                       return_reasons: bool = False, top_k: int = 0, top_p: float = 1.0):
+        """Generate for many prompts of unequal lengths; ``eos`` defaults to the configuration's stop tokens.
+        With a temperature above 0 tokens are sampled, among the ``top_k`` largest logits (0: all) and the
+        smallest set of them that holds ``top_p`` of the probability (1: all)."""
+        SamplingParams(temperature=temperature, seed=seed, top_k=top_k, top_p=top_p)        # checks the values
         stops = tuple(int(e) for e in (self.eos_token_id if eos is None else eos))
         requests = [Request(tuple(int(t) for t in p), int(max_tokens), float(temperature), int(seed), stops,
-                            ignore_eos, index) for index, p in enumerate(prompts)]
+                            ignore_eos, index, int(top_k), float(top_p)) for index, p in enumerate(prompts)]
         results: list[Generated] = run_requests(self.engine, requests, max_batch=self.max_batch, emit=emit)
         if return_reasons:
             return [r.tokens for r in results], [r.finish_reason for r in results]

@@ -6,7 +6,7 @@ ids (default 64) of ``{"holdout_ids": [...]}``; without ``--generate`` it scores
 next-token top-1 over ``--n-eval`` positions (default 500) with a sliding context
 and ``--dump`` writes the predictions one id per line (src/main.rs:3933-3941,
 4096-4104).  Here ``--model`` names a model folder (``--bundle`` is accepted for
-it), and ``--temperature``, ``--seed``, ``--eos``, ``--dtype`` and ``--prompts`` are
+it), and ``--temperature``, ``--seed``, ``--top-k``, ``--top-p``, ``--eos``, ``--dtype`` and ``--prompts`` are
 what a batch engine with sampling adds; ``--device cpu`` and ``--kv-int8`` are recognised and refused with a reason.  ``random`` writes a model folder with
 random weights, the counterpart of the reference's offline ``convert`` step.
 
@@ -80,6 +80,8 @@ def _main(argv: list[str] | None = None) -> int:
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     parser.add_argument("--temperature", type=float, default=0.0, help="0 picks the largest logit")
     parser.add_argument("--seed", type=int, default=0, help="seed of temperature sampling")
+    parser.add_argument("--top-k", type=int, default=0, help="sample among the k largest logits only (0: all)")
+    parser.add_argument("--top-p", type=float, default=1.0, help="sample among the smallest set of tokens holding this probability")
     parser.add_argument("--eos", default=None, help="stop token ids, comma separated (default: the config's; 'none')")
     parser.add_argument("--batch", type=int, default=64, help="most sequences in one batch")
     parser.add_argument("--device", default="auto", choices=["auto", "gpu", "cpu"],
@@ -126,7 +128,7 @@ def _main(argv: list[str] | None = None) -> int:
             ops.timing_start()
         started = time.perf_counter()
         outputs = lm.generate_batch(prompts, args.generate, eos=eos, temperature=args.temperature, seed=args.seed,
-                                    ignore_eos=(eos == []))
+                                    ignore_eos=(eos == []), top_k=args.top_k, top_p=args.top_p)
         seconds = time.perf_counter() - started
         if args.profile:
             report = ops.timing_report()

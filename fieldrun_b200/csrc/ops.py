@@ -29,7 +29,8 @@ _SIGNATURES = {
     "frb_expert_plan": "piiiippppppp",
     "frb_expert_combine": "pppiiip",
     "frb_expert_gemm_generic": "ppipppppipiiii",
-    "frb_sample_rows": "piippp",
+    "frb_sample_rows": "piipppp",
+    "frb_sample_floor": "piipppp",
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifii",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
@@ -297,11 +298,29 @@ def expert_gemm_generic(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch
 
 
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, floor: Optional[torch.Tensor] = None) -> None:
+    """out[r] = the largest logit of row r (the last index on ties), or where temperature[r] > 0 a sample of
+    softmax(logits[r] / temperature[r]) by inverse CDF with uniform[r]; ``floor[r]`` (from :func:`sample_floor`)
+    is the smallest logit that may be sampled."""
     _want(logits, torch.float32, "logits")
     _want(out, torch.int32, "picked tokens")
     rows, vocab = logits.shape
-    _call("frb_sample_rows", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(uniform), _ptr(out))
+    _call("frb_sample_rows", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(uniform), _ptr(floor), _ptr(out))
+
+
+def sample_floor(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+                 floor: torch.Tensor) -> None:
+    """floor[r] = the smallest logit of row r that stays when only the ``top_k[r]`` largest logits (0: all) and the
+    smallest set of them holding ``top_p[r]`` of the probability (1: all) may be sampled; equal logits stay or go
+    together.  -inf for greedy rows and rows that cut nothing."""
+    _want(logits, torch.float32, "logits")
+    _want(floor, torch.float32, "the sampling floor")
+    if top_k is not None:
+        _want(top_k, torch.int32, "top_k")
+    if top_p is not None:
+        _want(top_p, torch.float32, "top_p")
+    rows, vocab = logits.shape
+    _call("frb_sample_floor", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(floor))
 
 
 def gated_unit(both: torch.Tensor, out: torch.Tensor) -> None:

@@ -217,19 +217,29 @@ class Engine:
 
     # -- picking tokens ------------------------------------------------------------------------------------
     def pick(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
-             uniforms: Optional[Sequence[float]] = None) -> list[int]:
+             uniforms: Optional[Sequence[float]] = None, top_ks: Optional[Sequence[int]] = None,
+             top_ps: Optional[Sequence[float]] = None) -> list[int]:
         """One token per row of logits: the largest logit where the temperature is 0, else a sample with the
-        row's uniform number."""
+        row's uniform number, among the row's ``top_ks`` largest logits (0: all) and the smallest set of them
+        that holds ``top_ps`` of the probability (1: all)."""
         rows = logits.shape[0]
         # one more int: the kernels' status word comes to the host in the same copy as the tokens
         out = torch.empty(rows + 1, dtype=torch.int32, device=logits.device)
-        temp_dev = uni_dev = None
+        temp_dev = uni_dev = floor = None
+        logits = logits.contiguous()
         if temperatures is not None and any(t > 0 for t in temperatures):
             if uniforms is None or len(uniforms) != rows or len(temperatures) != rows:
                 raise StepError("sampling needs one temperature and one uniform number per row")
-            both = torch.tensor([list(temperatures), list(uniforms)], dtype=torch.float32).to(logits.device)
+            ks = list(top_ks) if top_ks is not None else [0] * rows
+            ps = list(top_ps) if top_ps is not None else [1.0] * rows
+            if len(ks) != rows or len(ps) != rows:
+                raise StepError("sampling needs one top_k and one top_p per row")
+            both = torch.tensor([list(temperatures), list(uniforms), ps], dtype=torch.float32).to(logits.device)
             temp_dev, uni_dev = both[0], both[1]
-        ops.sample_rows(logits.contiguous(), temp_dev, uni_dev, out[:rows])
+            if any(k > 0 for k in ks) or any(p < 1.0 for p in ps):
+                floor = torch.empty(rows, dtype=torch.float32, device=logits.device)
+                ops.sample_floor(logits, temp_dev, torch.tensor(ks, dtype=torch.int32).to(logits.device), both[2], floor)
+        ops.sample_rows(logits, temp_dev, uni_dev, out[:rows], floor)
         out[rows:].copy_(ops.tc_status(self.device))
         picked = out.tolist()
         ops.tc_status_raise(self.device, picked.pop())     # a kernel that gave up on a wait must not pass for a result

@@ -32,6 +32,8 @@ class Request:
     eos: tuple[int, ...] = ()
     ignore_eos: bool = False
     index: int = 0                    # the request's number: names it to ``emit`` and keys its random numbers
+    top_k: int = 0                    # sample among the k largest logits only (0: all)
+    top_p: float = 1.0                # ... and among the smallest set of them that holds this much probability
 
 
 @dataclass
@@ -109,6 +111,9 @@ def run_batch(engine, batch: Sequence[Request], emit: Optional[Callable[[int, in
         def pick(members, logits):
             temperatures = [batch[b].temperature for b in members]
             uniforms = [uniform(batch[b].seed, batch[b].index, len(results[b].tokens)) for b in members]
+            if any(batch[b].top_k > 0 or batch[b].top_p < 1.0 for b in members):
+                return engine.pick(logits, temperatures, uniforms, [batch[b].top_k for b in members],
+                                   [batch[b].top_p for b in members])
             return engine.pick(logits, temperatures, uniforms)
 
         # the prompts: one step, or several when they are many tokens; the first tokens are picked step by step

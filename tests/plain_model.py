@@ -259,6 +259,32 @@ def temperature_pick(logits_row, temperature, uniform):
     return min(idx, len(row) - 1)
 
 
+def sampling_floor(logits_row, temperature, top_k=0, top_p=1.0):
+    """The smallest logit that may be sampled: the top_k-th largest (top_k > 0), or the one with which the
+    probabilities of softmax(logits / temperature), taken in descending order, first add up to top_p
+    (top_p < 1), whichever is larger; -inf when neither cuts.  (Not in the reference, which is greedy only.)"""
+    row = np.asarray(logits_row, dtype=np.float64)
+    ordered = np.sort(row)[::-1]
+    floor = -np.inf
+    if top_k > 0:
+        floor = max(floor, ordered[min(top_k, len(row)) - 1])
+    if top_p < 1.0:
+        p = np.exp((ordered - ordered[0]) / float(temperature))
+        c = np.cumsum(p)
+        floor = max(floor, ordered[int(np.searchsorted(c, top_p * c[-1], side="left"))])
+    return floor
+
+
+def top_k_top_p_pick(logits_row, temperature, uniform, top_k=0, top_p=1.0):
+    """temperature_pick among the logits at or above sampling_floor; the others have no weight."""
+    row = np.asarray(logits_row, dtype=np.float64)
+    floor = sampling_floor(row, temperature, top_k, top_p)
+    p = np.where(row >= floor, np.exp((row - np.max(row)) / float(temperature)), 0.0)
+    c = np.cumsum(p)
+    idx = int(np.searchsorted(c, uniform * c[-1], side="right"))
+    return min(idx, len(row) - 1)
+
+
 def generate_greedy(config, W, prompt, max_new_tokens, eos=(), dtype=np.float64):
     """Greedy generation by full recompute, the reference's "naive" side (src/main.rs:3899-3901), with the stop
     rule of its stream loop: a stop token ends the sequence and is not part of the output

@@ -173,6 +173,17 @@ def test_temperature_sampling_repeats_with_its_seed_and_follows_the_plain_pick()
             row = pm.logits_all_positions(config, weights, seq)[-1]
             assert token == pm.temperature_pick(row, 0.8, uniform(5, index, step))
             seq.append(token)
+    # with only the largest logit kept, sampling is the greedy pick; with limits it follows the plain pick among the kept
+    assert lm.generate_batch(prompts, 6, eos=[], temperature=0.8, seed=5, top_k=1) == lm.generate_batch(prompts, 6, eos=[])
+    limited = lm.generate_batch(prompts, 8, eos=[], temperature=1.5, seed=9, top_k=12, top_p=0.7)
+    for index, (prompt, out) in enumerate(zip(prompts, limited)):
+        seq = list(prompt)
+        for step, token in enumerate(out):
+            row = pm.logits_all_positions(config, weights, seq)[-1]
+            assert token == pm.top_k_top_p_pick(row, 1.5, uniform(9, index, step), 12, 0.7)
+            seq.append(token)
+    with pytest.raises(ValueError):
+        lm.generate_batch(prompts, 2, temperature=0.8, top_p=0.0)
 
 
 def test_errors_come_before_any_launch():

@@ -41,7 +41,8 @@ class ScriptedEngine:
             rows.append(row)
         return np.stack(rows)
 
-    def pick(self, logits, temperatures=None, uniforms=None):
+    def pick(self, logits, temperatures=None, uniforms=None, top_ks=None, top_ps=None):
+        self.last_limits = (top_ks, top_ps)
         out = []
         for r, row in enumerate(logits):
             t = temperatures[r] if temperatures else 0.0
@@ -174,3 +175,12 @@ def test_many_prompt_tokens_are_run_in_several_steps():
     assert engine.steps[3] == [1, 1, 1, 1]
     for p, r in zip(prompts, results):
         assert r.tokens == expected(p, 4)
+
+
+def test_top_k_and_top_p_reach_the_pick():
+    engine = ScriptedEngine()
+    requests = [Request((1, 2), 2, temperature=0.7, seed=3, index=0, top_k=5, top_p=0.9), Request((3,), 2, temperature=0.7, index=1)]
+    run_batch(engine, requests)
+    assert engine.last_limits == ([5, 0], [0.9, 1.0])
+    run_batch(engine, [Request((1, 2), 2, temperature=0.7, index=0)])
+    assert engine.last_limits == (None, None)                      # nothing to cut: the plain call

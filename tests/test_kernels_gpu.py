@@ -807,3 +807,42 @@ def test_router_logits_in_float32(tokens, experts, width):
     logits = torch.full((tokens, experts), 7.0, dtype=torch.float32, device=DEV)
     ops().router_logits(dev(act), dev(router), logits)
     close(f64(logits), act.astype(np.float64) @ router.astype(np.float64).T, 2e-6, "router logits")
+
+
+@pytest.mark.parametrize("vocab", [37, 1000, 50001])
+def test_top_k_and_top_p_floor_and_picks(vocab):
+    rng = np.random.default_rng(40)
+    rows = 12
+    logits = (rng.normal(size=(rows, vocab)) * 3).astype(np.float32)
+    logits[3, : vocab // 2] = logits[3, vocab // 2: 2 * (vocab // 2)]          # a row of pairs of equal logits
+    temperature = np.array([0.7, 1.0, 1.3, 0.9, 0.5, 2.0, 1.0, 0.0, 1.1, 0.8, 1.0, 1.0], dtype=np.float32)
+    top_k = np.array([5, 0, 1, 4, 0, vocab, 20, 3, 0, 7, 2 * vocab, 1], dtype=np.int32)
+    top_p = np.array([1.0, 0.9, 1.0, 0.5, 0.3, 0.95, 0.8, 0.5, 1.0, 0.999, 0.5, 0.2], dtype=np.float32)
+    uniform = rng.random(size=rows).astype(np.float32)
+    floor = torch.full((rows,), 7.0, dtype=torch.float32, device=DEV)
+    ops().sample_floor(dev(logits), dev(temperature), dev(top_k), dev(top_p), floor)
+    picks = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample_rows(dev(logits), dev(temperature), dev(uniform), picks, floor)
+    got_floor, got = floor.cpu().numpy(), picks.tolist()
+    for r in range(rows):
+        row = logits[r].astype(np.float64)
+        if temperature[r] <= 0:
+            assert got_floor[r] == -np.inf and got[r] == pm.greedy_pick(logits[r])
+            continue
+        want = pm.sampling_floor(row, temperature[r], int(top_k[r]), float(top_p[r]))
+        if got_floor[r] != np.float32(want):
+            # float32 weights may put the crossing of top_p one logit further: the sum at that logit is then at the target
+            ordered = np.sort(row)[::-1]
+            c = np.cumsum(np.exp((ordered - ordered[0]) / temperature[r]))
+            at = min(int(np.searchsorted(-ordered, -float(got_floor[r]))), int(np.searchsorted(-ordered, -want)))
+            assert abs(c[at] - float(top_p[r]) * c[-1]) < 1e-4 * c[-1], (r, got_floor[r], want)
+            continue
+        kept = row >= want
+        assert kept.sum() >= 1 and (top_k[r] <= 0 or kept.sum() >= min(top_k[r], vocab) or top_p[r] < 1)
+        want_pick = pm.top_k_top_p_pick(row, temperature[r], uniform[r], int(top_k[r]), float(top_p[r]))
+        if got[r] != want_pick:                                        # float32 cumulative sums may differ by one place
+            p = np.where(kept, np.exp((row - row.max()) / temperature[r]), 0.0)
+            c = np.cumsum(p) / p.sum()
+            assert kept[got[r]] and (abs(c[got[r]] - uniform[r]) < 1e-5 or abs(c[max(got[r] - 1, 0)] - uniform[r]) < 1e-5), (r, got[r], want_pick)
+    # top_k = 1 is the largest logit whatever the uniform number
+    assert got[2] == int(np.argmax(logits[2])) and got[11] == int(np.argmax(logits[11]))

@@ -129,3 +129,16 @@ def test_greedy_generation_and_stop_rule(tmp_path):
     assert pm.generate_greedy(cfg, W, [3, 4, 5], 6, eos=(out[2],)) == out[:2]
     assert pm.greedy_pick([1.0, 3.0, 3.0, 2.0]) == 2              # the last of equal maxima
     assert pm.temperature_pick([0.0, 0.0, 0.0, 0.0], 1.0, 0.6) == 2
+
+
+def test_sampling_floor_and_pick_among_the_kept():
+    row = np.log(np.array([0.05, 0.4, 0.1, 0.25, 0.2]))
+    assert pm.sampling_floor(row, 1.0) == -np.inf
+    assert pm.sampling_floor(row, 1.0, top_k=2) == row[3]
+    assert pm.sampling_floor(row, 1.0, top_p=0.6) == row[3]          # 0.4 + 0.25 reaches 0.6
+    assert pm.sampling_floor(row, 1.0, top_p=0.66) == row[4]         # 0.65 does not reach 0.66: 0.2 stays too
+    assert pm.sampling_floor(row, 1.0, top_k=1, top_p=0.9) == row[1]
+    # among the kept {1, 3}: probabilities 0.4 / 0.65 and 0.25 / 0.65, in index order
+    assert pm.top_k_top_p_pick(row, 1.0, 0.5, top_k=2) == 1
+    assert pm.top_k_top_p_pick(row, 1.0, 0.7, top_k=2) == 3
+    assert pm.top_k_top_p_pick(row, 1.0, 0.999, top_p=0.6) == 3
