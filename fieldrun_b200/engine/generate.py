@@ -1,8 +1,9 @@
 """The generation loop above the step function.
 
 Requests are taken in order into batches; a batch's prompts run in one step (in
-several when together they pass ``PROMPT_TOKENS_PER_STEP``, so that a step's buffers stay
-bounded: a batch of 64 prompts of 2,048 tokens would otherwise need tens of GB of them),
+several when together they pass ``PROMPT_TOKENS_PER_STEP``, a longer prompt in pieces, so that
+a step's buffers stay bounded: a batch of 64 prompts of 2,048 tokens would otherwise need tens
+of GB of them),
 then every live sequence gets one token per step; a sequence that ends leaves
 the following steps; when the batch is done its slots go back and the next batch
 uses them.  Per sequence the rules are the reference's stream loop
@@ -46,20 +47,27 @@ class GenerationError(ValueError):
     pass
 
 
-PROMPT_TOKENS_PER_STEP = 16384      # most prompt tokens in one step, unless a single prompt is longer
+PROMPT_TOKENS_PER_STEP = 16384      # most prompt tokens in one step
 
 
-def prompt_steps(lengths: Sequence[int], budget: int) -> list[list[int]]:
-    """Cut a batch's prompts, in order, into steps of at most ``budget`` tokens (a longer prompt goes alone).
-    Returns lists of positions in ``lengths``."""
-    steps: list[list[int]] = []
-    current: list[int] = []
+def prompt_steps(lengths: Sequence[int], budget: int) -> list[list[tuple[int, int, int]]]:
+    """Cut a batch's prompts, in order, into steps of at most ``budget`` tokens.  A step is a list of pieces
+    ``(position in lengths, first token, end token)``; a prompt longer than the budget is run in pieces of the
+    budget, one step each (the cache keeps what the earlier pieces left, as in a decode step)."""
+    steps: list[list[tuple[int, int, int]]] = []
+    current: list[tuple[int, int, int]] = []
     held = 0
     for position, n in enumerate(lengths):
+        if n > budget:
+            if current:
+                steps.append(current)
+                current, held = [], 0
+            steps.extend([[(position, first, min(first + budget, n))] for first in range(0, n, budget)])
+            continue
         if current and held + n > budget:
             steps.append(current)
             current, held = [], 0
-        current.append(position)
+        current.append((position, 0, n))
         held += n
     if current:
         steps.append(current)
@@ -119,9 +127,13 @@ def run_batch(engine, batch: Sequence[Request], emit: Optional[Callable[[int, in
         # the prompts: one step, or several when they are many tokens; the first tokens are picked step by step
         budget = getattr(engine, "prompt_tokens_per_step", PROMPT_TOKENS_PER_STEP)
         picked: list[int] = []
-        for members in prompt_steps([len(batch[b].prompt) for b in live], budget):
-            group = [live[i] for i in members]
-            picked += pick(group, engine.step([slots[b] for b in group], [list(batch[b].prompt) for b in group]))
+        for pieces in prompt_steps([len(batch[b].prompt) for b in live], budget):
+            group = [live[i] for i, _, _ in pieces]
+            ends = [end == len(batch[b].prompt) for b, (_, _, end) in zip(group, pieces)]
+            logits = engine.step([slots[b] for b in group], [list(batch[b].prompt[first:end]) for b, (_, first, end) in zip(group, pieces)],
+                                 [[end - first - 1] if last else [] for (_, first, end), last in zip(pieces, ends)])
+            if all(ends):                                      # a piece that is not a prompt's last asks for no logits
+                picked += pick(group, logits)
         logits = None
         while live:
             if logits is not None:

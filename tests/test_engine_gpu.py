@@ -158,6 +158,21 @@ def test_greedy_generation_in_bfloat16_stays_on_the_plain_models_top():
         assert row[token] >= row.max() - 2 * TOLERANCE["bfloat16"] * np.abs(ref).max()
 
 
+def test_prompts_in_pieces_generate_what_whole_prompts_do():
+    """With a budget of 20 prompt tokens a step, prompts of 6 to 70 tokens run as whole prompts sharing steps and
+    as pieces of 20: the same tokens as with every prompt whole in one step."""
+    name = "b"
+    lm = loaded(name, "float32")
+    prompts = [request_tokens(name, n, 7) for n in (6, 70, 9, 45, 20)]
+    whole = lm.generate_batch(prompts, 6, eos=[])
+    budget = lm.engine.prompt_tokens_per_step
+    lm.engine.prompt_tokens_per_step = 20
+    try:
+        assert lm.generate_batch(prompts, 6, eos=[]) == whole
+    finally:
+        lm.engine.prompt_tokens_per_step = budget
+
+
 def test_temperature_sampling_repeats_with_its_seed_and_follows_the_plain_pick():
     from fieldrun_b200.sampling import uniform
     name = "a"

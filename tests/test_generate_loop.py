@@ -32,14 +32,17 @@ class ScriptedEngine:
         assert len(set(slots)) == len(slots)
         self.steps.append([len(t) for t in tokens])
         rows = []
-        for slot, new in zip(slots, tokens):
+        for b, (slot, new) in enumerate(zip(slots, tokens)):
             self.seqs[slot].extend(new)
+            if want is not None and list(want[b]) != [len(new) - 1]:
+                assert list(want[b]) == []                   # the loop asks for the last place or for nothing
+                continue
             nxt = (sum(self.seqs[slot]) + len(self.seqs[slot])) % self.vocab
             row = np.zeros(self.vocab, dtype=np.float32)
             row[nxt] = 5.0
             row[(nxt + 1) % self.vocab] = 4.0
             rows.append(row)
-        return np.stack(rows)
+        return np.stack(rows) if rows else None
 
     def pick(self, logits, temperatures=None, uniforms=None, top_ks=None, top_ps=None):
         self.last_limits = (top_ks, top_ps)
@@ -163,16 +166,16 @@ def test_sampling_is_per_request_not_per_batch_position():
 
 
 def test_many_prompt_tokens_are_run_in_several_steps():
-    assert prompt_steps([5, 5, 5], 10) == [[0, 1], [2]]
-    assert prompt_steps([50, 1, 1], 10) == [[0], [1, 2]]          # a prompt above the budget goes alone
-    assert prompt_steps([3], 10) == [[0]]
+    assert prompt_steps([5, 5, 5], 10) == [[(0, 0, 5), (1, 0, 5)], [(2, 0, 5)]]
+    assert prompt_steps([25, 1, 1], 10) == [[(0, 0, 10)], [(0, 10, 20)], [(0, 20, 25)], [(1, 0, 1), (2, 0, 1)]]   # a long prompt in pieces
+    assert prompt_steps([3], 10) == [[(0, 0, 3)]]
     engine = ScriptedEngine()
     engine.prompt_tokens_per_step = 10
-    prompts = [[1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11], [12, 13], [14] * 12]
+    prompts = [[1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11], [12, 13], [14] * 23]
     requests = [Request(tuple(p), 4, index=i) for i, p in enumerate(prompts)]
     results = run_batch(engine, requests)
-    assert engine.steps[:3] == [[6], [5, 2], [12]]                 # three prompt steps, then all four decode together
-    assert engine.steps[3] == [1, 1, 1, 1]
+    assert engine.steps[:5] == [[6], [5, 2], [10], [10], [3]]     # five prompt steps, then all four decode together
+    assert engine.steps[5] == [1, 1, 1, 1]
     for p, r in zip(prompts, results):
         assert r.tokens == expected(p, 4)
 
