@@ -29,17 +29,24 @@ __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
+__device__ __forceinline__ bool bar_try(uint32_t addr, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    return done != 0;
+}
+
+// Waits for the phase of the given parity.  The clock and the block's flag are only looked at when the
+// phase is not complete at the first try: most waits of a running pipeline are.
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
     const uint32_t addr = smem_addr(bar);
+    if (bar_try(addr, parity)) return true;
     const long long start = clock64();
     for (;;) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
+        if (bar_try(addr, parity)) return true;
         if (*failed || clock64() - start > FRB_TMA_WAIT_CYCLES) { *failed = 1; return false; }
     }
 }
