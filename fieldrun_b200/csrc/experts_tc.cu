@@ -121,7 +121,8 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     const int n = c0 + j;
                     if (n < rows) {
                         float v = __uint_as_float(gate[j]);
-                        if (PAIRED) v = v / (1.0f + expf(-v)) * __uint_as_float(up[j]);
+                        // silu(gate) * up; the result is rounded to bfloat16, so the fast exponential and division do
+                        if (PAIRED) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(up[j]);
                         out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
                     }
                 }
