@@ -110,20 +110,32 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (ok && !failed) {
             const int f = f0 + quarter * 32 + lane;
             OutT* out = (OutT*)p.out;
-            for (int c0 = 0; c0 < p.NT && c0 < rows; c0 += 16) {
-                uint32_t gate[16], up[16];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + c0;
-                tmem_ld16(taddr, gate);
-                if (PAIRED) tmem_ld16(taddr + p.NT, up);
-                tmem_wait_ld();
+            // 16 columns at a time, the next 16 on their way out of tensor memory while these are written
+            const uint32_t lanes = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int columns = min(p.NT, rows);
+            uint32_t gate[2][16], up[2][16];
+            tmem_ld16(lanes, gate[0]);
+            if (PAIRED) tmem_ld16(lanes + p.NT, up[0]);
+#pragma unroll 1
+            for (int c0 = 0; c0 < columns; c0 += 32) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int n = c0 + j;
-                    if (n < rows) {
-                        float v = __uint_as_float(gate[j]);
-                        // silu(gate) * up; the result is rounded to bfloat16, so the fast exponential and division do
-                        if (PAIRED) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(up[j]);
-                        out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
+                for (int half = 0; half < 2; ++half) {
+                    const int c = c0 + 16 * half;
+                    if (c >= columns) break;
+                    tmem_wait_ld();
+                    if (c + 16 < columns) {
+                        tmem_ld16(lanes + c + 16, gate[half ^ 1]);
+                        if (PAIRED) tmem_ld16(lanes + p.NT + c + 16, up[half ^ 1]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = c + j;
+                        if (n < rows) {
+                            float v = __uint_as_float(gate[half][j]);
+                            // silu(gate) * up; the result is rounded to bfloat16, so the fast exponential and division do
+                            if (PAIRED) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(up[half][j]);
+                            out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
+                        }
                     }
                 }
             }
