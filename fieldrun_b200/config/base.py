@@ -78,6 +78,38 @@ class KeyReader:
             raise ConfigError(f"{self.where}: key {name!r} must be a string, found {value!r}")
         return value
 
+    def present(self, name: str) -> bool:
+        """Whether ``name`` (dotted for a nested key) holds a value other than null."""
+        node: Any = self.raw
+        for piece in name.split("."):
+            if not isinstance(node, Mapping) or piece not in node or node[piece] is None:
+                return False
+            node = node[piece]
+        return True
+
+    def value(self, name: str) -> Any:
+        """The raw value under ``name`` (dotted for a nested key), or None."""
+        node: Any = self.raw
+        for piece in name.split("."):
+            if not isinstance(node, Mapping) or piece not in node or node[piece] is None:
+                return None
+            node = node[piece]
+        return node
+
+    def refuse_unless(self, name: str, allowed, meaning: str) -> None:
+        """A key that would change the arithmetic: if it is present its value must satisfy ``allowed``
+        (a predicate), else the configuration is refused with the key's name and ``meaning``."""
+        found = self.value(name)
+        if found is None:
+            return
+        try:
+            ok = bool(allowed(found))
+        except (TypeError, ValueError):
+            ok = False
+        if not ok:
+            raise ConfigError(f"{self.where}: key {name!r} is {found!r}: {meaning}")
+        self.used.add(name.split(".")[0])
+
     def integer_list(self, *names: str, default: Any = _MISSING) -> tuple[int, ...]:
         """An int or a list of ints (``eos_token_id`` is either, src/convert.rs:375-381)."""
         name, value = self._get(names, default)

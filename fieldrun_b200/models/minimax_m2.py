@@ -55,7 +55,7 @@ def minimax_m2_plan(cfg: MiniMaxM2Config) -> ModelPlan:
                 "top_k": cfg.num_experts_per_tok,
                 "expert_width": cfg.intermediate_size,
                 "score": "sigmoid",            # src/minimax.rs:95
-                "choice_bias": True,           # bias enters the choice only, src/minimax.rs:96-101
+                "choice_bias": cfg.use_routing_bias,   # the bias enters the choice only, src/minimax.rs:96-101
                 "renormalize": True,           # weights are sig / sum of picked sig, src/minimax.rs:100-103
                 "routed_scale": 1.0,
             },

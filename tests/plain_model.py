@@ -59,20 +59,26 @@ def sizes_from_config(c):
     nh = c["num_attention_heads"]
     d = c["hidden_size"]
     hd = c.get("head_dim") or d // nh
+    nested = c.get("rope_parameters") or {}
+    # the rotated share of a head: a count, or a factor at the top level or beside theta under rope_parameters
+    # (src/convert.rs:965-966 turns a factor into int(head_dim * factor); :610-615 looks under rope_parameters)
     if c.get("rotary_dim") is not None:
         rotary = c["rotary_dim"]
     elif c.get("partial_rotary_factor") is not None:
         rotary = int(hd * c["partial_rotary_factor"])
+    elif nested.get("partial_rotary_factor") is not None:
+        rotary = int(hd * nested["partial_rotary_factor"])
     else:
         rotary = hd
     theta = c.get("rope_theta")
     if theta is None:
-        theta = (c.get("rope_parameters") or {}).get("rope_theta", 10000.0)
+        theta = nested.get("rope_theta", 10000.0)
     return dict(
         layers=c["num_hidden_layers"], d=d, nh=nh, nkv=c.get("num_key_value_heads") or nh, hd=hd, rotary=rotary,
         theta=float(theta), eps=float(c.get("rms_norm_eps", 1e-6)), qk_norm=bool(c.get("use_qk_norm", True)),
         experts=c.get("num_local_experts") or c["num_experts"], top_k=c["num_experts_per_tok"],
         width=c["intermediate_size"], vocab=c["vocab_size"], tied=bool(c.get("tie_word_embeddings", False)),
+        routing_bias=bool(c.get("use_routing_bias", True)),
     )
 
 
@@ -189,8 +195,9 @@ def expert_swiglu(rows, w_gate, w_up, w_down):
 def routed_experts(a2, W, prefix, s, forced_ids=None, return_ids=False):
     """out[t] = sum over the picked experts, in rank order, of weight * expert(a2[t]) (src/minimax.rs:88-126)."""
     moe = prefix + "block_sparse_moe."
-    own_ids, _, margin = route(a2, W[moe + "gate.weight"], W[moe + "e_score_correction_bias"], s["top_k"])
-    ids, weights, _ = route(a2, W[moe + "gate.weight"], W[moe + "e_score_correction_bias"], s["top_k"], forced_ids)
+    bias = W[moe + "e_score_correction_bias"] if s.get("routing_bias", True) else 0.0
+    own_ids, _, margin = route(a2, W[moe + "gate.weight"], bias, s["top_k"])
+    ids, weights, _ = route(a2, W[moe + "gate.weight"], bias, s["top_k"], forced_ids)
     out = np.zeros_like(a2)
     for t in range(a2.shape[0]):
         for rank in range(s["top_k"]):

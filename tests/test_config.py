@@ -1,4 +1,5 @@
 import json
+import os
 
 import pytest
 
@@ -43,12 +44,110 @@ def test_missing_key_is_named(key):
 @pytest.mark.parametrize("change, word", [
     (dict(num_key_value_heads=3), "num_key_value_heads"), (dict(rotary_dim=7), "rotary_dim"),
     (dict(rotary_dim=18), "rotary_dim"), (dict(num_experts_per_tok=9), "num_experts_per_tok"),
-    (dict(eos_token_id=999), "eos_token_id"), (dict(hidden_size="64"), "hidden_size"),
+    (dict(hidden_size="64"), "hidden_size"),
     (dict(scoring_func="softmax"), "scoring_func"), (dict(rms_norm_eps=0), "rms_norm_eps"),
 ])
 def test_bad_values_are_named(change, word):
     with pytest.raises(ConfigError, match=word):
         fr.MiniMaxM2Config.from_dict({**CONFIG_A, **change})
+
+
+FIXTURES = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fixtures")
+
+
+def test_a_config_in_the_form_the_architectures_writer_emits(capsys):
+    """tests/fixtures/written_config_tiny.json has the keys and nesting that the architecture's own writer
+    produces for the tiny model of the reference's gate (scripts/gemma3_ref.py:61-77): theta and the rotary
+    share under ``rope_parameters``, the family's default stop token 200020 although the vocabulary is 64,
+    and bookkeeping keys the model has no use for."""
+    with open(os.path.join(FIXTURES, "written_config_tiny.json")) as handle:
+        raw = json.load(handle)
+    cfg = fr.MiniMaxM2Config.from_dict(raw)
+    assert "200020" in capsys.readouterr().err            # said once, then dropped
+    assert cfg.eos_token_id == ()
+    assert (cfg.vocab_size, cfg.hidden_size, cfg.num_hidden_layers) == (64, 32, 3)
+    assert (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim) == (4, 2, 8)
+    assert cfg.rotary_dim == 4 and cfg.rope_theta == 5e6 and cfg.rms_norm_eps == 1e-6
+    assert (cfg.num_local_experts, cfg.num_experts_per_tok, cfg.intermediate_size) == (8, 2, 16)
+    assert cfg.use_qk_norm and cfg.use_routing_bias and not cfg.tie_word_embeddings
+    # the plain implementation reads the same file on its own
+    import plain_model as pm
+    s = pm.sizes_from_config(raw)
+    assert (s["rotary"], s["theta"], s["hd"], s["nkv"], s["experts"], s["top_k"]) == (4, 5e6, 8, 2, 8, 2)
+
+
+def test_a_config_with_the_published_checkpoints_keys():
+    """The full-size form: ``rotary_dim`` and ``rope_theta`` at the top level, null stop tokens, and the
+    family's keys that this architecture fixes (all layers softmax attention, no shared expert, betas of 1)."""
+    with open(os.path.join(FIXTURES, "written_config_full_size.json")) as handle:
+        cfg = fr.MiniMaxM2Config.from_dict(json.load(handle))
+    assert (cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim) == (3072, 48, 8, 128)
+    assert (cfg.rotary_dim, cfg.rope_theta, cfg.rms_norm_eps) == (64, 5e6, 1e-6)
+    assert (cfg.num_local_experts, cfg.num_experts_per_tok, cfg.intermediate_size) == (256, 8, 1536)
+    assert (cfg.vocab_size, cfg.num_hidden_layers, cfg.eos_token_id) == (200064, 62, ())
+
+
+def test_the_rotary_share_in_each_of_its_spellings():
+    base = {k: v for k, v in CONFIG_A.items() if k not in ("rotary_dim", "rope_theta")}            # head_dim 16
+    assert fr.MiniMaxM2Config.from_dict(base).rotary_dim == 16
+    assert fr.MiniMaxM2Config.from_dict({**base, "rotary_dim": 8}).rotary_dim == 8
+    assert fr.MiniMaxM2Config.from_dict({**base, "partial_rotary_factor": 0.5}).rotary_dim == 8
+    nested = {**base, "rope_parameters": {"partial_rotary_factor": 0.5, "rope_theta": 123.0, "rope_type": "default"}}
+    cfg = fr.MiniMaxM2Config.from_dict(nested)
+    assert cfg.rotary_dim == 8 and cfg.rope_theta == 123.0
+    assert fr.MiniMaxM2Config.from_dict({**nested, "rotary_dim": 8}).rotary_dim == 8      # agreeing twice is fine
+    with pytest.raises(ConfigError, match="rotary share"):
+        fr.MiniMaxM2Config.from_dict({**nested, "rotary_dim": 16})
+    with pytest.raises(ConfigError, match="rotary share"):
+        fr.MiniMaxM2Config.from_dict({**nested, "partial_rotary_factor": 0.25})
+
+
+def test_stop_tokens_outside_the_vocabulary_are_dropped_not_refused(capsys):
+    cfg = fr.MiniMaxM2Config.from_dict({**CONFIG_A, "eos_token_id": [3, 999, 255, -1]})
+    assert cfg.eos_token_id == (3, 255)
+    err = capsys.readouterr().err
+    assert "999" in err and "-1" in err and err.count("\n") == 1
+
+
+@pytest.mark.parametrize("change, word", [
+    (dict(sliding_window=128), "sliding_window"),
+    (dict(rope_parameters={"rope_type": "yarn", "factor": 4.0}), "rope_type"),
+    (dict(rope_scaling={"type": "linear", "factor": 2.0}), "rope_scaling"),
+    (dict(shared_intermediate_size=64), "shared_intermediate_size"),
+    (dict(n_shared_experts=1), "n_shared_experts"),
+    (dict(norm_topk_prob=False), "norm_topk_prob"),
+    (dict(routed_scaling_factor=2.5), "routed_scaling_factor"),
+    (dict(scoring_func="softmax"), "scoring_func"),
+    (dict(hidden_act="gelu"), "hidden_act"),
+    (dict(attention_bias=True), "attention_bias"),
+    (dict(attn_type_list=[1, 0]), "attn_type_list"),
+    (dict(layer_types=["full_attention", "sliding_attention"]), "layer_types"),
+    (dict(qk_norm_type="per_head"), "qk_norm_type"),
+    (dict(layernorm_mlp_beta=0.5), "layernorm_mlp_beta"),
+    (dict(n_group=4), "n_group"),
+    (dict(final_logit_softcapping=30.0), "final_logit_softcapping"),
+])
+def test_keys_that_would_change_the_arithmetic_are_refused_by_name(change, word):
+    with pytest.raises(ConfigError, match=word):
+        fr.MiniMaxM2Config.from_dict({**CONFIG_A, **change})
+
+
+def test_the_same_keys_with_harmless_values_pass():
+    harmless = dict(sliding_window=None, rope_parameters={"rope_type": "default", "rope_theta": 10000.0},
+                    rope_scaling=None, shared_intermediate_size=0, norm_topk_prob=True, routed_scaling_factor=1.0,
+                    hidden_act="silu", attention_bias=False, attn_type_list=[1, 1], layernorm_mlp_beta=1.0,
+                    qk_norm_type="per_layer", n_group=1, final_logit_softcapping=None)
+    cfg = fr.MiniMaxM2Config.from_dict({**{k: v for k, v in CONFIG_A.items() if k != "rope_theta"}, **harmless})
+    assert cfg == fr.MiniMaxM2Config.from_dict(CONFIG_A)
+
+
+def test_a_model_without_a_routing_bias():
+    cfg = fr.MiniMaxM2Config.from_dict({**CONFIG_A, "use_routing_bias": False})
+    arch = architecture_for(CONFIG_A)
+    ff = arch.plan(cfg).layers[0].feed_forward
+    assert ff.args["choice_bias"] is False
+    names = [n.name for n in fr.build_model(arch, cfg, "float32").tensor_needs()]
+    assert not any("e_score_correction_bias" in n for n in names)
 
 
 def test_registry_by_architecture_and_model_type():
