@@ -2,9 +2,12 @@
 
 Each part lists its tensors as :class:`TensorNeed` (checkpoint name, shape,
 role).  Before any tensor is read the whole list is compared with the folder's
-index and one :class:`WeightError` reports every missing tensor, every tensor
-the model has no use for and every wrong shape -- the reference stops at the
+index and one :class:`WeightError` reports every missing tensor, every wrong
+shape and every stored type that cannot be read -- the reference stops at the
 first missing one (``convert: missing tensor``, src/convert.rs:70,85,95).
+Tensors the model has no use for (rotary buffers, heads of other tasks) are
+listed in one warning on stderr: the reference fetches by name and never looks
+at the rest (src/convert.rs:1231-1257).  ``strict=True`` makes them an error too.
 
 Precision.  A ``matrix`` (an operand of a tensor-core product: projections,
 experts, embedding, head) is held in bfloat16 when the model runs in bfloat16,
@@ -17,6 +20,7 @@ three stored types).
 """
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 from typing import Callable, Iterable, Mapping, Protocol
 
@@ -65,8 +69,10 @@ _REAL = {"F32", "F16", "BF16", "F64"}
 _INTEGER = {"I32", "I64", "U8"}
 
 
-def check_needs(where: str, needs: Iterable[TensorNeed], found: Mapping[str, tuple[str, tuple[int, ...]]]) -> None:
-    """Raise one WeightError unless ``found`` (name -> (dtype tag, shape)) is exactly what ``needs`` lists."""
+def check_needs(where: str, needs: Iterable[TensorNeed], found: Mapping[str, tuple[str, tuple[int, ...]]],
+                strict: bool = False) -> list[str]:
+    """Raise one WeightError unless ``found`` (name -> (dtype tag, shape)) holds everything ``needs`` lists, in
+    the right shapes and readable types.  Returns the names the model has no use for (an error if ``strict``)."""
     wanted: dict[str, TensorNeed] = {}
     for need in needs:
         other = wanted.get(need.name)
@@ -85,8 +91,9 @@ def check_needs(where: str, needs: Iterable[TensorNeed], found: Mapping[str, tup
         allowed = _INTEGER if need.role == TABLE else _REAL
         if tag not in allowed:
             wrong_dtype.append((name, tag))
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    if missing or wrong_shape or wrong_dtype or (strict and unexpected):
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_dtype)
+    return unexpected
 
 
 def held_dtype(role: str, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
@@ -104,10 +111,13 @@ class FolderSource:
     """Tensors of a model folder, validated against the model's needs up front."""
 
     def __init__(self, model_dir: str, needs: Iterable[TensorNeed], compute_dtype: torch.dtype,
-                 device: torch.device | str):
+                 device: torch.device | str, strict: bool = False):
         self.folder = ModelFolder(model_dir)
         found = {n: (e.dtype_tag, e.shape) for n, e in self.folder.entries.items()}
-        check_needs(model_dir, needs, found)
+        self.unused = check_needs(model_dir, needs, found, strict)
+        if self.unused:
+            shown = ", ".join(self.unused[:8]) + (f", ... ({len(self.unused)} in all)" if len(self.unused) > 8 else "")
+            print(f"{model_dir}: warning: tensors the model has no use for are left unread: {shown}", file=sys.stderr)
         self.compute_dtype = compute_dtype
         self.device = torch.device(device)
 

@@ -1,5 +1,6 @@
 """Shared pieces of the GPU tests: model folders in temporary places, plain logits, comparisons."""
 import functools
+import json
 import os
 import tempfile
 
@@ -7,7 +8,7 @@ import numpy as np
 
 import fieldrun_b200 as fr
 import plain_model as pm
-from tiny_configs import ALL
+from tiny_configs import ALL, WRITTEN_AS_IS
 
 # largest allowed |engine - plain| as a share of the largest |plain logit| of the compared rows
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
@@ -20,6 +21,9 @@ def model_folder(name: str) -> str:
     config, init = ALL[name]
     folder = os.path.join(_ROOT, name)
     fr.write_random_model(folder, config, init)
+    if name in WRITTEN_AS_IS:
+        with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as handle:
+            json.dump(WRITTEN_AS_IS[name], handle, indent=1)
     return folder
 
 

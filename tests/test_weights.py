@@ -80,6 +80,44 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert word in text
 
 
+def test_tensors_the_model_has_no_use_for_are_a_warning_unless_strict(tmp_path, capsys):
+    """The reference fetches by name and ignores the rest (src/convert.rs:1231-1257)."""
+    folder = _folder(tmp_path)
+    tensors = {k: torch.from_numpy(v) for k, v in read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(4)
+    tensors["model.mtp.0.weight"] = torch.zeros(2, 2)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+    source = FolderSource(folder, _needs(folder), torch.float32, "cpu")
+    assert sorted(source.unused) == ["model.layers.0.self_attn.rotary_emb.inv_freq", "model.mtp.0.weight"]
+    source.close()
+    err = capsys.readouterr().err
+    assert "warning" in err and "inv_freq" in err and "model.mtp.0.weight" in err
+    with pytest.raises(WeightError, match="unexpected \\(2\\)"):
+        FolderSource(folder, _needs(folder), torch.float32, "cpu", strict=True)
+
+
+def test_random_elements_are_a_function_of_seed_name_and_index():
+    """Each element restated with Python integers: two rounds of the hash, eight 16-bit fields, one scale."""
+    from fieldrun_b200.weights.random_init import _GOLDEN, _MASK, _UNIT, _mix_int, tensor_key, unit_normal
+    key = tensor_key(7, "model.layers.3.block_sparse_moe.experts.11.w2.weight")
+    assert key != tensor_key(8, "model.layers.3.block_sparse_moe.experts.11.w2.weight")
+    assert key != tensor_key(7, "model.layers.3.block_sparse_moe.experts.12.w2.weight")
+    drawn = unit_normal(key, (37, 5), "cpu", scale=0.02)
+
+    def element(i):
+        a = _mix_int((i * _GOLDEN + key) & _MASK)
+        b = _mix_int(a)
+        total = sum((word >> shift) & 0xFFFF for word in (a, b) for shift in (0, 16, 32, 48))
+        return np.float32(2 * total - 8 * 65535) * np.float32(_UNIT * 0.02)
+
+    for i in (0, 1, 36, 100, 184):
+        assert drawn.flatten()[i].item() == float(element(i))
+    # a slice is re-made without the rest; chunks do not show
+    assert torch.equal(unit_normal(key, (20,), "cpu", scale=0.02, first=100), drawn.flatten()[100:120])
+    big = unit_normal(key, (1 << 18,), "cpu")
+    assert abs(big.mean().item()) < 0.01 and abs(big.std().item() - 1.0) < 0.01 and big.abs().max().item() < 4.9
+
+
 def test_integer_tensor_where_a_real_one_is_needed():
     with pytest.raises(WeightError, match="unsupported dtype: w is stored as I32"):
         check_needs("here", [TensorNeed("w", (2,), VECTOR)], {"w": ("I32", (2,))})

@@ -1,6 +1,9 @@
 """Small configurations of the architecture for the tests.  They differ from one another in every
 size and option: head counts and groups, head size, rotary share, theta, q/k norm on and off, experts
 and top-k, expert width, vocabulary (one is prime), eps, tied head, and the spread of the weights."""
+import json
+import os
+
 import torch
 
 from fieldrun_b200 import RandomInit
@@ -37,4 +40,14 @@ CONFIG_D = dict(
     num_experts_per_tok=2, intermediate_size=128, vocab_size=300, rms_norm_eps=1e-6, tie_word_embeddings=False)
 INIT_D = RandomInit(seed=3, matrix_std=0.04, norm_std=0.1, bias_std=0.05)
 
-ALL = {"a": (CONFIG_A, INIT_A), "b": (CONFIG_B, INIT_B), "c": (CONFIG_C, INIT_C), "d": (CONFIG_D, INIT_D)}
+# the tiny model of the reference's own gate (scripts/gemma3_ref.py:61-77: vocab 64, hidden 32, 3 layers, 4 heads
+# over 2, head size 8, 8 experts, 2 per token, width 16), its config.json in the form the architecture's writer
+# emits (theta and the rotary share under rope_parameters, a stop token outside the vocabulary), and the gate's
+# recipe for the weights: norm weights N(0, 0.1) around ZERO and a routing bias N(0, 0.2) (:223-247)
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "fixtures", "written_config_tiny.json")) as _handle:
+    CONFIG_E = json.load(_handle)
+INIT_E = RandomInit(seed=4, matrix_std=0.02, norm_std=0.1, norm_mean=0.0, bias_std=0.2, stored_dtype=torch.float32)
+# folders of these configurations keep the config.json as it is written here, key for key
+WRITTEN_AS_IS = {"e": CONFIG_E}
+
+ALL = {"e": (CONFIG_E, INIT_E), "a": (CONFIG_A, INIT_A), "b": (CONFIG_B, INIT_B), "c": (CONFIG_C, INIT_C), "d": (CONFIG_D, INIT_D)}
