@@ -5,10 +5,13 @@
 
 Prints one JSON line.  A step is one decode step of a batch of --batch sequences (default 8) whose
 prompts of 2,048 tokens were run first; `value` is decoded tokens a second with the tokens staying on the
-device, `e2e` the same through the Python entry point with host tokens in and out every step.  It also
-times a prefill of one 2,048-token prompt and decode steps at batch 1 and 64 (their prompts are run too).  With --gpus above 1 it
-says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference
-cannot run here.
+device, `e2e` the same through the Python entry point with host tokens in and out every step, `e2e_loop`
+whole calls of `generate_batch` (prompts included).  It also times a prefill of one 2,048-token prompt, decode
+steps at batch 1 and 64 (their prompts are run too), all three batch sizes again in mid-run (contexts of 3,072),
+each with the bytes its step has to read and the fraction of the memory roofline, and (`long_cache`) a batch of
+8 sequences of 8,192 to 65,536 tokens: their prompts and decode steps over those caches.  With --gpus above 1
+it says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference cannot
+run here.
 """
 from __future__ import annotations
 
@@ -31,6 +34,8 @@ M2 = dict(
 FULL_LAYERS = 16
 PROMPT = 2048
 CONTEXT = 4096
+MID_RUN = 3072                                   # context of the mid-run points (decoding runs from 2,048 to 4,096)
+LONG_PROMPTS = tuple(8192 * i for i in range(1, 9))   # the long-cache batch: 8,192 to 65,536 tokens
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -113,6 +118,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=FULL_LAYERS)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="leave out prefill and the batch 1/64 points")
+    parser.add_argument("--skip-long-cache", action="store_true", help="leave out the batch of 8,192 to 65,536 tokens")
+    parser.add_argument("--skip-loop", action="store_true", help="leave out the generate_batch timings")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -139,6 +146,8 @@ def main() -> int:
     config = dict(M2, num_hidden_layers=args.layers)
     largest = max(args.batch, 1 if args.skip_points else 64)
     max_tokens = largest * CONTEXT + 2 * CONTEXT
+    if not args.skip_long_cache:
+        max_tokens = max(max_tokens, sum(LONG_PROMPTS) + len(LONG_PROMPTS) * 512)
     t0 = time.time()
     lm = fr.random_model(config, fr.RandomInit(seed=2, matrix_std=0.02, norm_std=0.1, bias_std=0.01), dtype="bfloat16",
                          max_tokens=max_tokens, num_slots=largest + 2, max_batch=largest)
@@ -151,13 +160,14 @@ def main() -> int:
     def prompts(n, length):
         return [rng.integers(0, cfg.vocab_size, size=length).tolist() for _ in range(n)]
 
-    def fill(batch):
-        """Sequences holding PROMPT tokens each, by running their prompts (eight prompts a step)."""
+    def fill(batch, length=PROMPT):
+        """Sequences holding ``length`` tokens each, by running their prompts (16,384 prompt tokens a step)."""
         slots = [engine.new_sequence() for _ in range(batch)]
         first = torch.empty(batch, dtype=torch.int32, device="cuda")
-        for at in range(0, batch, 8):
-            part = slots[at:at + 8]
-            logits = engine.step(part, prompts(len(part), PROMPT))
+        per_step = max(1, 16384 // length)
+        for at in range(0, batch, per_step):
+            part = slots[at:at + per_step]
+            logits = engine.step(part, prompts(len(part), length))
             ops.sample_rows(logits.contiguous(), None, None, first[at:at + len(part)])
         return slots, first
 
@@ -177,8 +187,21 @@ def main() -> int:
             tokens = device_step(slots, tokens)
         stop.record()
         torch.cuda.synchronize()
-        ops.tc_status_check(engine.device)               # no kernel of the timed steps gave up on a wait
+        engine.check()                                   # no kernel of the timed steps gave up on a wait
         return start.elapsed_time(stop) / steps, ops.launches() - before, tokens
+
+    def point(batch, length, steps, warmup=3):
+        """Decode at ``batch`` from prompts of ``length``: tokens a second, bytes a step must read, roofline share."""
+        slots, first = fill(batch, length)
+        lo = engine.cache.length(slots[0]) + warmup
+        ms, _, _ = time_decode(slots, first, steps, warmup)
+        step_bytes, picked = decode_bytes(slots)
+        for s in slots:
+            engine.release(s)
+        gbs = step_bytes / (ms * 1e-3) / 1e9
+        return {"tok_s": round(batch * 1000.0 / ms, 2), "ms": round(ms, 4), "bytes": step_bytes, "gbs": round(gbs, 1),
+                "frac": round(gbs / peak["hbm_gbs"], 4), "experts": round(sum(picked) / max(len(picked), 1), 1),
+                "contexts": f"{lo}..{lo + steps}"}
 
     def decode_bytes(slots):
         """Bytes one decode step has to read: every weight it uses once (the experts actually picked, per
@@ -205,6 +228,7 @@ def main() -> int:
 
     # ---- the headline: decode at --batch ------------------------------------------------------------------
     slots, first = fill(args.batch)
+    timed_contexts = f"{PROMPT + args.warmup}..{PROMPT + args.warmup + args.steps}"
     timed_from = time.time()
     ms_step, launches, tokens = time_decode(slots, first, args.steps, args.warmup)
     clocks = sampler.window(timed_from, time.time())
@@ -238,7 +262,7 @@ def main() -> int:
             "head_dim": cfg.head_dim, "rotary_dim": cfg.rotary_dim, "experts": cfg.num_local_experts,
             "top_k": cfg.num_experts_per_tok, "expert_width": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
-            "l2": "weights read per step exceed L2", "peaks": peak_source,
+            "l2": "weights read per step exceed L2", "peaks": peak_source, "timed_contexts": timed_contexts,
         },
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": 4 * args.batch + 4 * (7 * args.batch + 1), "d2h_bytes_per_step": 4 * args.batch},
@@ -276,16 +300,78 @@ def main() -> int:
                              "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "flops": flops,
                              "weight_bytes": prefill_bytes,
                              "hbm_frac": round(prefill_bytes / (prefill_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
-        # ---- decode at batch 1 and 64 ------------------------------------------------------------------------
-        points = {}
-        for batch in (1, 64):
-            slots, first = fill(batch)
-            ms, _, _ = time_decode(slots, first, max(8, args.steps // 2), 3)
-            points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 2)
-            for s in slots:
-                engine.release(s)
-        points[f"decode_b{args.batch}"] = round(value, 2)
+        # ---- decode at batch 1 and 64, and every batch size again in mid-run ------------------------------------
+        points = {f"decode_b{args.batch}": round(value, 2), f"decode_b{args.batch}_frac": round(achieved / peak["hbm_gbs"], 4),
+                  f"decode_b{args.batch}_gbs": round(achieved, 1), f"decode_b{args.batch}_bytes": step_bytes,
+                  f"decode_b{args.batch}_experts": round(sum(picked) / max(len(picked), 1), 1),
+                  f"decode_b{args.batch}_contexts": timed_contexts}
+        half = max(8, args.steps // 2)
+        for batch, length, tag in [(1, PROMPT, ""), (64, PROMPT, "")] + [(b, MID_RUN, "_mid") for b in (1, args.batch, 64)]:
+            got = point(batch, length, half)
+            name = f"decode_b{batch}{tag}"
+            points[name] = got["tok_s"]
+            for key in ("frac", "gbs", "bytes", "experts", "contexts"):
+                points[f"{name}_{key}"] = got[key]
         result["points"] = points
+
+    if not args.skip_loop:
+        # ---- whole calls of generate_batch: prompts, picks and host decisions included ---------------------------
+        loop = {}
+        for tag, lengths in (("equal", [64] * args.batch), ("ragged", [8 + (56 * i) // max(args.batch - 1, 1) for i in range(args.batch)])):
+            from fieldrun_b200.engine.generate import Request, generate
+            best = None
+            for attempt in range(2):                                  # the first call records the decode steps it needs
+                requests = [Request(tuple(p), n, ignore_eos=True, index=i)
+                            for i, (p, n) in enumerate(zip(prompts(args.batch, PROMPT), lengths))]
+                torch.cuda.synchronize()
+                begin = time.perf_counter()
+                out = generate(engine, requests, max_batch=args.batch)
+                torch.cuda.synchronize()
+                best = time.perf_counter() - begin
+            made = sum(len(r.tokens) for r in out)
+            loop[f"{tag}_tok_s"] = round(made / best, 1)
+            loop[f"{tag}_s"] = round(best, 4)
+            loop[f"{tag}_new_tokens"] = made
+        loop["prompts"] = f"{args.batch} x {PROMPT}"
+        loop["what"] = "generate_batch wall time, prompts included; equal: 64 new tokens each; ragged: 8 to 64"
+        result["e2e_loop"] = loop
+
+    if not args.skip_long_cache:
+        # ---- a batch of long sequences: prompts of 8,192 to 65,536 tokens in steps of 16,384, then decode steps -------
+        from fieldrun_b200.engine.generate import prompt_steps
+        slots = [engine.new_sequence() for _ in LONG_PROMPTS]
+        ids = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in LONG_PROMPTS]
+        first = torch.empty(len(slots), dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for pieces in prompt_steps(list(LONG_PROMPTS), engine.prompt_tokens_per_step):
+            group = [i for i, _, _ in pieces]
+            ends = [end == LONG_PROMPTS[i] for i, _, end in pieces]
+            logits = engine.step([slots[i] for i in group], [ids[i][lo:hi] for i, lo, hi in pieces],
+                                 [[hi - lo - 1] if last else [] for (_, lo, hi), last in zip(pieces, ends)])
+            if logits is not None:
+                done = [i for i, last in zip(group, ends) if last]
+                picked_now = engine.pick_on_device(logits)
+                first[torch.tensor(done, device="cuda")] = picked_now
+        stop.record()
+        torch.cuda.synchronize()
+        engine.check()
+        prompt_s = start.elapsed_time(stop) / 1000.0
+        long_steps = max(8, args.steps // 2)
+        ms, _, _ = time_decode(slots, first, long_steps, 3)
+        step_bytes, picked = decode_bytes(slots)
+        kv_bytes = sum(engine.cache.length(s) for s in slots) * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * len(model.blocks)
+        for s in slots:
+            engine.release(s)
+        result["long_cache"] = {
+            "batch": len(LONG_PROMPTS), "prompt_tokens": sum(LONG_PROMPTS), "shortest": LONG_PROMPTS[0], "longest": LONG_PROMPTS[-1],
+            "layers": args.layers, "layers_of_config": 4, "prompt_s": round(prompt_s, 3),
+            "prompt_tok_s": round(sum(LONG_PROMPTS) / prompt_s, 1), "decode_ms": round(ms, 4),
+            "decode_tok_s": round(len(LONG_PROMPTS) * 1000.0 / ms, 2), "decode_steps_timed": long_steps,
+            "cache_gb": round(kv_bytes / 1e9, 2), "bytes_per_step": step_bytes,
+            "gbs": round(step_bytes / (ms * 1e-3) / 1e9, 1), "frac": round(step_bytes / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4),
+            "experts": round(sum(picked) / max(len(picked), 1), 1)}
 
     sampler.stop()
     print(json.dumps(result))

@@ -96,7 +96,9 @@ class LanguageModel:
         """float32 logits [len(ids), vocab] of every position of one sequence run whole."""
         slot = self.engine.new_sequence()
         try:
-            return self.engine.step([slot], [list(ids)], [list(range(len(ids)))])
+            out = self.engine.step([slot], [list(ids)], [list(range(len(ids)))])
+            self.engine.check()                 # a kernel that gave up on a wait must not pass for a result
+            return out
         finally:
             self.engine.release(slot)
 

@@ -11,8 +11,8 @@ a store, a page pool and a table of its own; a windowed group gives a page back
 as soon as every key on it lies outside the window.  What is cached is K after
 norm and rotary and V as projected (src/minimax.rs:262-268).
 
-The state area holds, per cache line that asks for one, a float32 tensor of a
-fixed shape per slot, zeroed when the slot is given out.  MiniMax-M2 has no such
+The state area holds, per cache line that asks for one, a tensor of a fixed
+shape and type per slot, zeroed when the slot is given out.  MiniMax-M2 has no such
 state; mixers with a recurrence use it.
 """
 from __future__ import annotations
@@ -26,6 +26,7 @@ import torch
 from .pools import CacheFull, IndexPool
 
 PAGE_TOKENS = 64
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
 
 
 @dataclass(frozen=True)
@@ -35,7 +36,8 @@ class CacheNeed:
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None            # None: every earlier key stays visible
-    state_shape: tuple[int, ...] = ()    # float32 state per sequence; () for none
+    state_shape: tuple[int, ...] = ()    # state per sequence; () for none
+    state_dtype: str = "float32"         # "float32" | "bfloat16" | "int32"
 
     @property
     def group_key(self) -> tuple[int, int, int | None] | None:
@@ -54,7 +56,7 @@ class LineView:
     values: torch.Tensor | None          # [num_pages, kv_heads, head_dim, PAGE_TOKENS]
     page_table: torch.Tensor | None      # int32 [num_slots, max_pages]; -1 where no page is held
     window: int | None
-    state: torch.Tensor | None           # float32 [num_slots, *state_shape]
+    state: torch.Tensor | None           # [num_slots, *state_shape] in the need's state_dtype
 
 
 class _Group:
@@ -67,6 +69,7 @@ class _Group:
         self.first_page = np.zeros(num_slots, dtype=np.int64)        # first page index still held
         self.end_page = np.zeros(num_slots, dtype=np.int64)          # one past the last page held
         self.dirty: list[tuple[int, int, int]] = []
+        self.fresh: list[int] = []           # pages given out since the last sync whose old contents may be read
         shape = (len(self.lines), num_pages, self.kv_heads, PAGE_TOKENS, self.head_dim)
         if allocate:
             self.keys = torch.zeros(shape, dtype=dtype, device=device)
@@ -88,6 +91,11 @@ class _Group:
             self.table[slot, index] = self.pool.alloc()
         self.end_page[slot] = hi
         self.dirty.append((slot, lo, hi))
+        # A page that the new tokens do not fill keeps, beyond them, what an earlier sequence left there.  The
+        # attention kernels give such keys no weight, but 0 x NaN is NaN: whatever was there must be finite.
+        # So the last page handed out is cleared unless the sequence's tokens fill it to the end.
+        if new_len % PAGE_TOKENS:
+            self.fresh.append(int(self.table[slot, hi - 1]))
 
     def release_outside_window(self, slot: int, length: int) -> None:
         if self.window is None:
@@ -118,7 +126,15 @@ class _Group:
         if self.table_dev is not None:
             for slot, lo, hi in self.dirty:
                 self.table_dev[slot, lo:hi].copy_(torch.from_numpy(self.table[slot, lo:hi]))
+            if len(self.fresh) == 1:
+                self.keys[:, self.fresh[0]].zero_()
+                self.values[:, self.fresh[0]].zero_()
+            elif self.fresh:
+                pages = torch.tensor(self.fresh, dtype=torch.int64).to(self.keys.device)
+                self.keys.index_fill_(1, pages, 0)
+                self.values.index_fill_(1, pages, 0)
         self.dirty.clear()
+        self.fresh.clear()
 
 
 class SequenceCache:
@@ -151,7 +167,11 @@ class SequenceCache:
         self.states: dict[int, torch.Tensor] = {}
         for line, need in enumerate(self.needs):
             if need.state_shape:
-                self.states[line] = torch.zeros((self.num_slots, *need.state_shape), dtype=torch.float32,
+                if need.state_dtype not in _STATE_DTYPES:
+                    raise ValueError(f"cache line {line}: a state of type {need.state_dtype!r}; "
+                                     f"known: {sorted(_STATE_DTYPES)}")
+                self.states[line] = torch.zeros((self.num_slots, *need.state_shape),
+                                                dtype=_STATE_DTYPES[need.state_dtype],
                                                 device=self.device if allocate else "cpu")
 
     # -- slots ------------------------------------------------------------------------------------

@@ -293,7 +293,9 @@ __global__ void __launch_bounds__(HD) attention_decode_tma_merge_kernel(DecodeTm
     const int pos = p.seq_pos[b];
     const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int keys_per_block = params.chunks_per_block * ATT_CHUNK;
-    const int first = lo_key / keys_per_block, last = pos / keys_per_block;
+    // never beyond the partial results the launch has room for, whatever the position says
+    const int last = min(pos / keys_per_block, p.max_chunks - 1), first = min(lo_key / keys_per_block, last);
+    if (pos / keys_per_block >= p.max_chunks && d == 0) atomicExch(params.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
     float top = -INFINITY;
     for (int c = first; c <= last; ++c) top = fmaxf(top, p.part_ml[(row0 + c) * 2]);
@@ -334,7 +336,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
-    p.num_kv_heads = num_kv_heads; p.max_chunks = parts;
+    p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status;
     params.chunks_per_block = chunks_per_block; params.status = status;
     dim3 grid(parts, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
     const size_t smem = (size_t)DT_STAGES * FRB_PAGE * head_dim * 2 + 1024;

@@ -5,10 +5,10 @@
 FRB_API int frb_attention_decode_mma(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                                      int max_pages, const int* seq_pos, const int* seq_slot, float* part_o, float* part_ml,
                                      void* out, int num_seqs, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                     int window, int max_chunks, cudaStream_t stream) {
+                                     int window, int max_chunks, int* status, cudaStream_t stream) {
     return launch_attention_decode("attention_decode_mma", q, k_pages, v_pages, page_table, max_pages, seq_pos, seq_slot,
                                    part_o, part_ml, out, num_seqs, num_heads, num_kv_heads, head_dim, scale, window,
-                                   max_chunks, stream);
+                                   max_chunks, stream, status);
 }
 
 // ----------------------------------------------------------------------------- many tokens per sequence

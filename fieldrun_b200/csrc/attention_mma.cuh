@@ -185,7 +185,10 @@ struct DecodeAttnParams {
     bf16* out;                 // [B, nh * HD]
     float scale2;
     int window, max_pages, num_heads, num_kv_heads, max_chunks;
+    int* status;               // null, or a word that gets FRB_STATUS_TOO_LONG when a sequence has more chunks than max_chunks
 };
+
+#define FRB_STATUS_TOO_LONG 5
 
 // grid (chunk, kv head, sequence), 4 warps.  Rows of the tile are the query heads of the kv head's group.
 // Each warp takes one page of the chunk: scores, softmax within the page, then P V in two halves of the
@@ -324,7 +327,10 @@ __global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnPa
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int pos = p.seq_pos[b];
     const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int first = lo_key / ATT_CHUNK, last = pos / ATT_CHUNK;
+    // never beyond the partial results the launch has room for, whatever the position says (the caller's
+    // max_chunks covers the longest sequence; a smaller one must not make this read another row's results)
+    const int last = min(pos / ATT_CHUNK, p.max_chunks - 1), first = min(lo_key / ATT_CHUNK, last);
+    if (pos / ATT_CHUNK >= p.max_chunks && p.status && d == 0) atomicExch(p.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
     float top = -INFINITY;
     for (int c = first; c <= last; ++c) top = fmaxf(top, p.part_ml[(row0 + c) * 2]);
@@ -342,7 +348,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
                                           const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                           float* part_o, float* part_ml, void* out, int num_seqs, int num_heads,
                                           int num_kv_heads, int head_dim, float scale, int window, int max_chunks,
-                                          cudaStream_t stream) {
+                                          cudaStream_t stream, int* status = nullptr) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -354,7 +360,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
-    p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks;
+    p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks; p.status = status;
     dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
 #define FRB_LAUNCH_DECODE(HD)                                                       \
     launch_dependent(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), 0, stream, p);                   \

@@ -214,6 +214,7 @@ struct QkvParams {
     float eps;
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
     int num_tokens, v_tiles;  // v_tiles: blocks beyond the tokens' own write the values, 64 tokens of one kv head each
+    int per_head;             // the norm weights are [head_dim] and every head has a statistic of its own
 };
 
 #define QKV_BATCH 8          // elements a thread loads before it uses any of them
@@ -233,6 +234,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     const int half = p.rotary_dim / 2;
     float* s_cos = raw + all_width;
     float* s_sin = s_cos + half;
+    float* s_sq = s_sin + half;              // per-head norm only: the squares [qk_width], then 1/rms of every head
+    float* s_rinv = s_sq + qk_width;
     const InT* src = (const InT*)p.qkv + (size_t)t * all_width;
     const WT* qw = (const WT*)p.q_weight;
     const WT* kw = (const WT*)p.k_weight;
@@ -247,8 +250,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
             const int i = base + u * NORM_BLOCK + threadIdx.x;
             v[u] = i < all_width ? to_f32<InT>(src[i]) : 0.f;
             w[u] = 1.f;
-            if (i < q_width) { if (qw) w[u] = to_f32<WT>(qw[i]); }
-            else if (i < qk_width) { if (kw) w[u] = to_f32<WT>(kw[i - q_width]); }
+            if (i < q_width) { if (qw) w[u] = to_f32<WT>(qw[p.per_head ? i % hd : i]); }
+            else if (i < qk_width) { if (kw) w[u] = to_f32<WT>(kw[p.per_head ? (i - q_width) % hd : i - q_width]); }
         }
 #pragma unroll
         for (int u = 0; u < QKV_BATCH; ++u) {
@@ -256,6 +259,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
             if (i < all_width) raw[i] = v[u] * w[u];
             if (i < q_width) ssq += v[u] * v[u];
             else if (i < qk_width) ssk += v[u] * v[u];
+            if (p.per_head && i < qk_width) s_sq[i] = v[u] * v[u];
         }
     }
     const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
@@ -266,16 +270,27 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
     const int in_page = pos % FRB_PAGE;
     float rinv_q = 1.f, rinv_k = 1.f;
-    if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
-    if (kw) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
+    if (qw && !p.per_head) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
+    if (kw && !p.per_head) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
     __syncthreads();
+    if (p.per_head) {
+        // one statistic per head (q heads, then k heads): a warp sums a head's squares in a fixed order
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (int h = warp; h < p.num_heads + p.num_kv_heads; h += NORM_BLOCK / 32) {
+            float ss = 0.f;
+            for (int d = lane; d < hd; d += 32) ss += s_sq[h * hd + d];
+            ss = warp_sum(ss);
+            if (lane == 0) s_rinv[h] = (h < p.num_heads ? qw : kw) ? 1.0f / sqrtf(ss / (float)hd + p.eps) : 1.f;
+        }
+        __syncthreads();
+    }
 
     for (int i = threadIdx.x; i < qk_width; i += NORM_BLOCK) {
         const bool is_q = i < q_width;
         const float* base = is_q ? raw : raw + q_width;
-        const float rinv = is_q ? rinv_q : rinv_k;
         const int local = is_q ? i : i - q_width;
         const int head = local / hd, dim = local - head * hd;
+        const float rinv = p.per_head ? s_rinv[(is_q ? 0 : p.num_heads) + head] : (is_q ? rinv_q : rinv_k);
         float value = base[local] * rinv;
         if (dim < p.rotary_dim) {
             int j, partner;
@@ -433,7 +448,7 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
                             const int* tok_pos, const int* tok_slot, const int* page_table, int max_pages,
                             void* q_out, void* k_pages, void* v_pages, int out_dtype, int num_tokens, int num_heads,
                             int num_kv_heads, int head_dim, int rotary_dim, int interleaved, int write_cache,
-                            cudaStream_t stream) {
+                            int per_head, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     FRB_CHECK_ARG(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "qkv_prepare: rotary_dim %d must be even and <= head_dim %d",
                   rotary_dim, head_dim);
@@ -444,13 +459,15 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.v_pages = v_pages; p.eps = eps; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
     p.rotary_dim = rotary_dim; p.interleaved = interleaved; p.max_pages = max_pages; p.write_cache = write_cache;
     p.table_positions = table_positions;
-    p.num_tokens = num_tokens; p.v_tiles = 0;
-    const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim) * sizeof(float);
+    p.num_tokens = num_tokens; p.v_tiles = 0; p.per_head = per_head && (q_weight || k_weight);
+    // per-head statistics: the squares of the q and k rows and one factor per head beside the rows
+    const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim +
+                         (p.per_head ? (size_t)(num_heads + num_kv_heads) * (head_dim + 1) : 0)) * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + 2 kv heads) * head_dim = %d needs more than 200 KB of shared memory",
                   (num_heads + 2 * num_kv_heads) * head_dim);
     const int in_bytes = in_dtype == FRB_F32 ? 4 : 2, out_bytes = out_dtype == FRB_F32 ? 4 : 2, w_bytes = weight_dtype == FRB_F32 ? 4 : 2;
     const auto aligned = [](const void* ptr, int bytes) { return ((uintptr_t)ptr & (size_t)(4 * bytes - 1)) == 0; };
-    const bool by_four = head_dim % 4 == 0 && rotary_dim % (interleaved ? 4 : 8) == 0 && aligned(qkv, in_bytes) &&
+    const bool by_four = !p.per_head && head_dim % 4 == 0 && rotary_dim % (interleaved ? 4 : 8) == 0 && aligned(qkv, in_bytes) &&
                          aligned(q_out, out_bytes) && aligned(k_pages, out_bytes) && aligned(q_weight, w_bytes) &&
                          aligned(k_weight, w_bytes);
     FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {

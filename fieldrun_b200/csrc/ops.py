@@ -22,7 +22,8 @@ _P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlon
 _SIGNATURES = {
     "frb_embed_rows": "ppipiii",
     "frb_rmsnorm": "pppppippifiipipi",
-    "frb_qkv_prepare": "pippifppipppipppiiiiiiii",
+    "frb_qkv_prepare": "pippifppipppipppiiiiiiiii",
+    "frb_wait_probe": "lpp",
     "frb_add_rows": "ppl",
     "frb_attention_generic": "pppipipppiiiifi",
     "frb_router_topk": "ppiiiifpp",
@@ -32,7 +33,7 @@ _SIGNATURES = {
     "frb_sample_rows": "piipppp",
     "frb_sample_floor": "piipppp",
     "frb_gated_unit": "ppiii",
-    "frb_attention_decode_mma": "ppppipppppiiiifii",
+    "frb_attention_decode_mma": "ppppipppppiiiifiip",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
     "frb_attention_decode_tma": "pppipipppppiiiifiiip",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
@@ -189,6 +190,9 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> 
     _call("frb_embed_rows", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), tokens.numel(), width, vocab)
 
 
+NORM_MAX_SUMMED_ROWS = 32      # most weighted rows per token that the norm kernel sums itself (NORM_MAX_TOP_K)
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
             out32: Optional[torch.Tensor] = None, write_back: bool = False,
@@ -227,8 +231,10 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
                 cos_table: Optional[torch.Tensor], sin_table: Optional[torch.Tensor], tok_pos: torch.Tensor,
                 tok_slot: torch.Tensor, page_table: Optional[torch.Tensor], q_out: torch.Tensor,
                 k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], *, num_heads: int,
-                num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, write_cache: bool) -> None:
-    """Full-width Q/K RMSNorm (when weights are given), rotary from the tables, Q out, K/V into their pages."""
+                num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, write_cache: bool,
+                per_head: bool = False) -> None:
+    """Q/K RMSNorm (when weights are given: over the whole row with weights [heads * head_dim], or with
+    ``per_head`` over each head with weights [head_dim]), rotary from the tables, Q out, K/V into their pages."""
     if (q_weight is None) != (k_weight is None):
         raise KernelError("q and k norm weights come together or not at all")
     wdtype = q_weight.dtype if q_weight is not None else torch.float32
@@ -244,7 +250,7 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
     _call("frb_qkv_prepare", _ptr(qkv), _code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _code(wdtype), float(eps),
           _ptr(cos_table), _ptr(sin_table), table_positions, _ptr(tok_pos), _ptr(tok_slot), _ptr(page_table), max_pages,
           _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(out_dtype), qkv.shape[0], num_heads, num_kv_heads, head_dim,
-          rotary_dim, int(interleaved), int(write_cache))
+          rotary_dim, int(interleaved), int(write_cache), int(per_head))
 
 
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
@@ -344,7 +350,20 @@ def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _want(part_o, torch.float32, "partial outputs")
     _call("frb_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
           _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads, num_kv_heads,
-          head_dim, float(scale), int(window or 0), max_chunks)
+          head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)))
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the device (asked once per device)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _SM_COUNT[index]
 
 
 def decode_chunks_per_block(num_seqs: int, num_kv_heads: int, max_chunks: int, sms: int = 148) -> int:
@@ -371,7 +390,7 @@ def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want(part_o, torch.float32, "partial outputs")
     if chunks_per_block is None:
-        chunks_per_block = decode_chunks_per_block(q.shape[0], num_kv_heads, max_chunks)
+        chunks_per_block = decode_chunks_per_block(q.shape[0], num_kv_heads, max_chunks, sm_count(q.device))
     _call("frb_attention_decode_tma", _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads,
           num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, int(chunks_per_block),
@@ -448,6 +467,24 @@ def stream_shape(tiles: int, features: int, inner: int, tile_rows: int, paired: 
 
 
 _TC_STATUS: dict[str, torch.Tensor] = {}
+# what each code of the status word means: which wait of which kernel gave up
+_WAIT_CODES = {
+    1: "expert products: the producer waiting for a free stage",
+    2: "expert products: the MMA thread waiting for a loaded stage",
+    3: "expert products: the epilogue waiting for the accumulators",
+    4: "one-token attention: waiting for a page's copy",
+    5: "one-token attention: a sequence has more keys than the launch was sized for (max_chunks); keys were left out",
+    11: "prompt attention: the producer waiting for a free key/value stage",
+    12: "prompt attention: the query tile's copy",
+    13: "prompt attention: the MMA thread waiting for a loaded key/value stage",
+    14: "prompt attention: the MMA thread waiting for a free score buffer",
+    15: "prompt attention: the MMA thread waiting for the probabilities",
+    16: "prompt attention: the softmax waiting for the scores",
+    17: "prompt attention: the softmax waiting for the product before last",
+    18: "prompt attention: the correction waiting for the last product",
+    19: "prompt attention: the epilogue waiting for the last product",
+    99: "the wait probe, whose wait is meant to run out",
+}
 
 
 def tc_status(device) -> torch.Tensor:
@@ -470,10 +507,8 @@ def tc_status_raise(device, code: int) -> None:
     """Raise for a status word that was read from the device (0: nothing happened) and clear the word."""
     if code != 0:
         _TC_STATUS[str(device)].zero_()
-        where = {1: "the producer waiting for a free stage", 2: "the MMA thread waiting for a loaded stage",
-                 3: "the epilogue waiting for the accumulators",
-                 4: "one-token attention waiting for a page's copy"}.get(code, f"code {code}")
-        raise KernelError(f"a tensor-core kernel's wait gave up ({where}); the step's results are not valid")
+        where = _WAIT_CODES.get(code, f"code {code}")
+        raise KernelError(f"a kernel gave up instead of finishing ({where}); the step's results are not valid")
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -533,3 +568,13 @@ def attention_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           page_table.shape[1], _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start),
           _ptr(seq_q_len), _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0),
           _ptr(tc_status(q.device)))
+
+
+def wait_probe(device, limit_cycles: int = 100_000) -> int:
+    """Launch the one block whose wait is meant to run out after ``limit_cycles`` clock cycles: it leaves code
+    99 in the device's status word (see :func:`tc_status_check`).  Returns the cycles it waited.  For testing
+    the way from a device-side give-up to the host-side error; nothing faults and nothing is left pending."""
+    waited = torch.zeros(1, dtype=torch.int64, device=device)
+    with torch.cuda.device(device):
+        _call("frb_wait_probe", int(limit_cycles), _ptr(tc_status(device)), _ptr(waited))
+    return int(waited.item())

@@ -41,13 +41,15 @@ __device__ __forceinline__ bool bar_try(uint32_t addr, uint32_t parity) {
 
 // Waits for the phase of the given parity.  The clock and the block's flag are only looked at when the
 // phase is not complete at the first try: most waits of a running pipeline are.
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+// `limit`: clock cycles after which the wait gives up (about a second by default).
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* failed,
+                                         long long limit = FRB_TMA_WAIT_CYCLES) {
     const uint32_t addr = smem_addr(bar);
     if (bar_try(addr, parity)) return true;
     const long long start = clock64();
     for (;;) {
         if (bar_try(addr, parity)) return true;
-        if (*failed || clock64() - start > FRB_TMA_WAIT_CYCLES) { *failed = 1; return false; }
+        if (*failed || clock64() - start > limit) { *failed = 1; return false; }
     }
 }
 

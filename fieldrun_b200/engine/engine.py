@@ -21,7 +21,17 @@ from .context import StepContext, Workspace, pack_tables
 from .model import DecoderModel
 
 RECORD_KV_STEP = 1024          # a recorded step serves lengths up to the next multiple of this
-RECORDED_STEPS_KEPT = 6
+RECORDED_STEPS_KEPT = 24       # recorded steps kept; beyond that the one unused for longest goes
+# batch sizes that steps are recorded for; a step of another size runs in the next larger one (see _recorded_step)
+RECORD_BATCHES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+
+def record_batch(batch: int) -> int:
+    """The batch size of the recorded step that a decode step of ``batch`` sequences runs in."""
+    for size in RECORD_BATCHES:
+        if size >= batch:
+            return size
+    return (batch + 255) // 256 * 256
 
 
 class StepError(ValueError):
@@ -54,15 +64,28 @@ class _RecordedStep:
         self.copied = torch.cuda.Event()
 
     def load(self, tokens, slots: Sequence[int], starts: Sequence[int]) -> None:
-        """New inputs: ``tokens`` from the host (numpy) or already on the device (tensor)."""
+        """New inputs: ``tokens`` from the host (numpy) or already on the device (tensor).  Fewer sequences
+        than the recorded batch: the last one is repeated in the rows left over.  A repeated row computes what
+        its original computes, bit for bit, writes the same key and value to the same place, picks the same
+        experts (so no weight is read that the step would not read anyway) and its logits are never looked at."""
+        real = len(slots)
+        pad = self.batch - real
+        if pad:
+            slots = list(slots) + [slots[-1]] * pad
+            starts = list(starts) + [starts[-1]] * pad
         self.copied.synchronize()                          # the last copy out of the pinned buffer is done
         self.host[self.batch:] = torch.from_numpy(pack_tables(slots, starts, [1] * self.batch))
         if isinstance(tokens, torch.Tensor):
             self.tables.copy_(self.host[self.batch:], non_blocking=True)
             if tokens.data_ptr() != self.tokens.data_ptr():
-                self.tokens.copy_(tokens)
+                self.tokens[:real].copy_(tokens)
+            if pad:
+                self.tokens[real:].copy_(self.tokens[real - 1:real].expand(pad))
         else:
-            self.host[:self.batch] = torch.from_numpy(np.asarray(tokens).astype(np.int32))
+            flat = np.asarray(tokens).astype(np.int32)
+            self.host[:real] = torch.from_numpy(flat)
+            if pad:
+                self.host[real:self.batch] = int(flat[-1])
             self.inputs.copy_(self.host, non_blocking=True)
         self.copied.record()
 
@@ -80,8 +103,9 @@ class Engine:
         self.vocab_size = model.plan.vocab_size
         self.steps_run = 0
         self.record_steps = record_steps and model.replayable
-        self._recorded: dict[tuple[int, int], _RecordedStep] = {}
+        self._recorded: dict[tuple[int, int], _RecordedStep] = {}      # in order of last use, oldest first
         self.steps_replayed = 0
+        self.steps_recorded = 0
         # most prompt tokens that the generation loop puts into one step (a step's buffers grow with its tokens)
         self.prompt_tokens_per_step = 16384
 
@@ -168,7 +192,7 @@ class Engine:
             raise StepError(f"a sequence would pass position {self.cache.max_tokens}, where the position tables end")
         self.cache.begin_step(slots, ones)
         if self.record_steps:
-            logits = self._recorded_step(slots, tokens, starts, keep=False)
+            logits = self._recorded_step(slots, tokens, starts, keep=False)[:len(slots)]
         else:
             ctx = StepContext(self.workspace, self.model.dtype, slots, starts, ones)
             rows = torch.arange(len(slots), dtype=torch.int32, device=self.device)
@@ -176,6 +200,13 @@ class Engine:
         self.cache.end_step(slots, ones)
         self.steps_run += 1
         return logits
+
+    def check(self) -> None:
+        """Raise if a kernel's bounded wait gave up since the last check (its results are then not valid).
+        This reads one int from the device, so it waits for the work before it.  ``step`` checks after a
+        prompt and ``pick`` with every token it brings to the host; a loop that stays on the device
+        (``step_on_device``/``pick_on_device``) or reads logits only calls this once it is through."""
+        ops.tc_status_check(self.device)
 
     def pick_on_device(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The largest logit of every row, as an int32 tensor on the device."""
@@ -185,22 +216,28 @@ class Engine:
         return out
 
     def _recorded_step(self, slots: Sequence[int], tokens, starts: Sequence[int], keep: bool = True) -> torch.Tensor:
-        """A step of one token per sequence with the logits of every sequence wanted: recorded at its first
-        occurrence for this batch size and length range, replayed afterwards.  With ``keep`` the logits are
-        copied out of the recorded step's own buffer, which the next replay overwrites."""
+        """A step of one token per sequence with the logits of every sequence wanted, run from a recording.
+
+        Steps are recorded per (batch size, length range): batch sizes come from ``RECORD_BATCHES`` and a
+        step of another size runs in the next larger recording with its last sequence repeated, so a batch
+        whose sequences end one after another goes through a dozen recordings, not one per size.  A
+        recording is made at its key's first occurrence; ``RECORDED_STEPS_KEPT`` are kept, by last use.
+        With ``keep`` the logits are copied out of the recorded step's own buffer, which the next replay
+        overwrites."""
         batch = len(slots)
         longest = max(starts) + 1
         kv_cap = min((longest + RECORD_KV_STEP - 1) // RECORD_KV_STEP * RECORD_KV_STEP, self.cache.max_tokens)
-        key = (batch, kv_cap)
-        step = self._recorded.get(key)
+        key = (record_batch(batch), kv_cap)
+        step = self._recorded.pop(key, None)
         if step is None:
-            if len(self._recorded) >= RECORDED_STEPS_KEPT:
+            while len(self._recorded) >= RECORDED_STEPS_KEPT:
                 self._recorded.pop(next(iter(self._recorded)))
-            step = self._recorded[key] = _RecordedStep(self, batch, kv_cap)
+            step = _RecordedStep(self, key[0], kv_cap)
+        self._recorded[key] = step                          # the most recently used is last
         step.load(tokens, slots, starts)
         if step.graph is None:
             # run it directly this once (this also sizes every scratch buffer), then record it for the next times
-            logits = self.model.forward(step.ctx, self.cache, step.tokens, step.rows).clone()
+            logits = self.model.forward(step.ctx, self.cache, step.tokens, step.rows)[:batch].clone()
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launches()
@@ -209,11 +246,12 @@ class Engine:
             step.kernels = ops.launches() - before
             ops.count_launches(-step.kernels)              # recorded, not run
             step.graph = graph
+            self.steps_recorded += 1
             return logits
         step.graph.replay()
         ops.count_launches(step.kernels)
         self.steps_replayed += 1
-        return step.logits.clone() if keep else step.logits
+        return step.logits[:batch].clone() if keep else step.logits[:batch]
 
     # -- picking tokens ------------------------------------------------------------------------------------
     def pick(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,

@@ -5,8 +5,8 @@ several when together they pass ``PROMPT_TOKENS_PER_STEP``, a longer prompt in p
 a step's buffers stay bounded: a batch of 64 prompts of 2,048 tokens would otherwise need tens
 of GB of them),
 then every live sequence gets one token per step; a sequence that ends leaves
-the following steps; when the batch is done its slots go back and the next batch
-uses them.  Per sequence the rules are the reference's stream loop
+the following steps and gives its slot and pages back at once; the next batch
+starts when the last sequence of this one has ended and uses the freed slots.  Per sequence the rules are the reference's stream loop
 (src/minimax.rs:441-461): a stop token ends the sequence *before* it is put out,
 the caller's ``emit`` may end it by returning False, and it ends at
 ``max_new_tokens``.  With ``ignore_eos`` it is the reference's fixed-length
@@ -155,6 +155,9 @@ def run_batch(engine, batch: Sequence[Request], emit: Optional[Callable[[int, in
                     continue
                 still.append(b)
                 feed.append([token])
+            for b in live:
+                if b not in still:
+                    engine.release(slots.pop(b))              # an ended sequence holds nothing any longer
             live = still
             if live:
                 logits = engine.step([slots[b] for b in live], feed)

@@ -1,8 +1,10 @@
 """Grouped-query attention over the paged cache.
 
-q, k, v = act W^T without bias; optionally one RMSNorm over the whole Q row and
-one over the whole K row ("full_width", before the head split and the rotary,
-src/minimax.rs:136-138); rotary on the first ``rotary_dim`` dims of each head at
+q, k, v = act W^T without bias; optionally an RMSNorm of q and of k before the
+rotary: "full_width", one statistic over the whole Q row and one over the whole
+K row with weights as wide as the rows (before the head split,
+src/minimax.rs:136-138), or "per_head", a statistic per head with one weight
+vector of the head's size for all heads; rotary on the first ``rotary_dim`` dims of each head at
 the token's absolute position; K (normed, rotated) and V written to the cache
 line; every query head h attends, with keys of head h // (heads / kv_heads), over
 the keys it may see; output projection without bias (src/minimax.rs:253-282).
@@ -35,8 +37,8 @@ class GQAAttention(Mixer):
         self.num_kv_heads = int(a["num_kv_heads"])
         self.head_dim = int(a["head_dim"])
         self.qk_norm = a.get("qk_norm", "none")
-        if self.qk_norm not in ("none", "full_width"):
-            raise ValueError(f"qk_norm {self.qk_norm!r} is neither 'none' nor 'full_width'")
+        if self.qk_norm not in ("none", "full_width", "per_head"):
+            raise ValueError(f"qk_norm {self.qk_norm!r} is none of 'none', 'full_width', 'per_head'")
         self.qk_norm_eps = float(a.get("qk_norm_eps", 1e-6))
         self.softmax_scale = float(a.get("softmax_scale", self.head_dim ** -0.5))
         self.window = a.get("window")
@@ -69,6 +71,9 @@ class GQAAttention(Mixer):
         if self.qk_norm == "full_width":
             needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.q_width,), VECTOR, "around_one")
             needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.kv_width,), VECTOR, "around_one")
+        elif self.qk_norm == "per_head":
+            needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.head_dim,), VECTOR, "around_one")
+            needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.head_dim,), VECTOR, "around_one")
         return needs
 
     def tensor_needs(self):
@@ -78,7 +83,7 @@ class GQAAttention(Mixer):
         needs = self._needs()
         self.w_qkv = torch.cat([source.fetch(needs[n]) for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
         self.w_o = source.fetch(needs["o_proj"])
-        if self.qk_norm == "full_width":
+        if self.qk_norm != "none":
             self.q_norm = source.fetch(needs["q_norm"])
             self.k_norm = source.fetch(needs["k_norm"])
 
@@ -89,7 +94,7 @@ class GQAAttention(Mixer):
 
     def prepare(self, num_positions: int, device) -> None:
         if self.position is not None and self.position.rotary_dim > 0:
-            self.cos, self.sin = self.position.tables(num_positions, device)
+            self.cos, self.sin = self.position.shared_tables(num_positions, device)
 
     # -- one step --------------------------------------------------------------------------------------
     def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
@@ -101,7 +106,7 @@ class GQAAttention(Mixer):
                         line.page_table, q, line.keys, line.values, num_heads=self.num_heads,
                         num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=rotary_dim,
                         interleaved=bool(self.position.interleaved) if self.position is not None else False,
-                        write_cache=writes_cache)
+                        write_cache=writes_cache, per_head=self.qk_norm == "per_head")
         out = ctx.buffer("attention.out", (tokens, self.q_width), self.dtype)
         self.attend(ctx, q, line, out)
         return linear(out, self.w_o)

@@ -21,6 +21,8 @@ Interfaces
 """
 from __future__ import annotations
 
+import json
+import weakref
 from typing import Any, Callable, Mapping, Optional
 
 import torch
@@ -59,10 +61,32 @@ class Part:
 
 class DeferredUpdate:
     """An update of the residual stream that its maker has not summed up yet, so that the norm which adds it
-    can do the sum while it reads the stream.  ``materialize`` gives the plain float32 tensor [T, width]."""
+    can do the sum while it reads the stream.  ``materialize`` gives the plain float32 tensor [T, width]; any
+    norm can take any deferred update that way."""
 
     def materialize(self, ctx) -> torch.Tensor:
         raise NotImplementedError
+
+
+class WeightedRows(DeferredUpdate):
+    """The one deferred form that norms may sum themselves: update[t] = sum over r < k, in the order of r, of
+    ``weights[t, r] * rows[row_map[t * k + r]]`` (float32 ``rows`` [N, width], float32 ``weights`` [T, k],
+    int32 ``row_map`` [T * k]).  Any part may make one: routed experts do (a token's experts in rank order,
+    src/minimax.rs:121-123), and so may a mixer that blends several candidates per token.  A norm that
+    cannot take it, or not with this ``k``, calls ``materialize``."""
+
+    def __init__(self, rows: torch.Tensor, weights: torch.Tensor, row_map: torch.Tensor):
+        self.rows, self.weights, self.row_map = rows, weights, row_map
+
+    @property
+    def top_k(self) -> int:
+        return int(self.weights.shape[-1])
+
+    def materialize(self, ctx) -> torch.Tensor:
+        from ..csrc import ops
+        out = ctx.buffer("weighted_rows.sum", (self.weights.shape[0], self.rows.shape[1]), torch.float32)
+        ops.expert_combine(self.rows, self.weights, self.row_map, out)
+        return out
 
 
 def as_tensor(ctx, update):
@@ -79,13 +103,24 @@ class Norm(Part):
 
 
 class Position:
-    """A position encoding handed to a mixer: it fills the tables the mixer's kernel rotates with."""
+    """A position encoding handed to a mixer: it fills the tables the mixer's kernel rotates with.
+    ``build_position`` gives mixers whose position arguments are equal one and the same object, and
+    ``shared_tables`` makes that object's tables once per (length, device): the layers of a model read one
+    pair of tables, not one pair each."""
 
     rotary_dim: int = 0
     interleaved: bool = False
 
     def tables(self, num_positions: int, device) -> tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
         raise NotImplementedError
+
+    def shared_tables(self, num_positions: int, device) -> tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        made = self.__dict__.setdefault("_tables_made", {})
+        key = (int(num_positions), str(torch.device(device)))
+        if key not in made:
+            made.clear()                      # one length at a time: a model's cache is sized once
+            made[key] = self.tables(num_positions, device)
+        return made[key]
 
 
 class Mixer(Part):
@@ -151,10 +186,26 @@ def build_part(category: str, spec: PartSpec, dtype: torch.dtype):
     return _factory(category, spec.kind)(spec, dtype)
 
 
+_POSITIONS: "weakref.WeakValueDictionary[str, Position]" = weakref.WeakValueDictionary()
+
+
 def build_position(args: Optional[Mapping[str, Any]]) -> Optional[Position]:
+    """The position encoding of ``args``; equal arguments give the same object while a mixer still holds it."""
     if not args:
         return None
-    return _factory("position", args["kind"])(args)
+    factory = _factory("position", args["kind"])
+    try:
+        key = f"{id(factory)}:" + json.dumps(dict(args), sort_keys=True, default=repr)
+    except (TypeError, ValueError):
+        return factory(args)
+    position = _POSITIONS.get(key)
+    if position is None:
+        position = factory(args)
+        try:
+            _POSITIONS[key] = position
+        except TypeError:                     # an object that cannot be weakly referenced is simply not shared
+            pass
+    return position
 
 
 def build_block(kind: str, mixer, feed_forward, mixer_norm, feed_forward_norm) -> Block:

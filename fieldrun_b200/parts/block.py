@@ -12,6 +12,8 @@ class PreNormBlock(Block):
             pending = as_tensor(ctx, pending)
         act, _ = self.mixer_norm.forward(ctx, x, delta=pending)
         update = self.mixer.forward(ctx, act, line, writes_cache)
+        if not self.feed_forward_norm.accepts_deferred:
+            update = as_tensor(ctx, update)
         act2, act2_32 = self.feed_forward_norm.forward(ctx, x, delta=update,
                                                        want32=self.feed_forward.wants_float32_input)
         return x, self.feed_forward.forward_deferred(ctx, act2, act2_32)

@@ -17,24 +17,11 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
-from .base import DeferredUpdate, FeedForward, register_part
+from .base import FeedForward, WeightedRows, register_part
 from .linear import linear
 
 TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
 TENSOR_CORE_ROWS_PER_EXPERT = 12     # above this many rows per expert (on average) a step runs on tcgen05
-
-
-class ExpertUpdate(DeferredUpdate):
-    """The outputs of each token's experts, not yet summed: update[t] = sum over ranks r, in rank order, of
-    weights[t, r] * y[row_of_assign[t * k + r]]."""
-
-    def __init__(self, y: torch.Tensor, weights: torch.Tensor, row_of_assign: torch.Tensor):
-        self.y, self.weights, self.row_of_assign = y, weights, row_of_assign
-
-    def materialize(self, ctx) -> torch.Tensor:
-        out = ctx.buffer("experts.out", (self.weights.shape[0], self.y.shape[1]), torch.float32)
-        ops.expert_combine(self.y, self.weights, self.row_of_assign, out)
-        return out
 
 
 class RoutedExperts(FeedForward):
@@ -60,6 +47,9 @@ class RoutedExperts(FeedForward):
         self.w13: Optional[torch.Tensor] = None
         self.w2: Optional[torch.Tensor] = None
         self.on_route = None              # called with the picked ids [T, k] of every step (for measurements)
+        # int32 [rows >= T, k] on the device, or None: when set, every step copies its picked ids into the first
+        # T rows.  The copy is a device operation, so unlike ``on_route`` it also happens in a recorded step.
+        self.route_log: Optional[torch.Tensor] = None
 
     def _expert_needs(self, e: int) -> tuple[TensorNeed, TensorNeed, TensorNeed]:
         d, i = self.hidden_size, self.expert_width
@@ -206,6 +196,12 @@ class RoutedExperts(FeedForward):
                                  p["num_tiles"])
         return ids, weights, p
 
+    def _tell_route(self, ids: torch.Tensor) -> None:
+        if self.on_route is not None:
+            self.on_route(ids)
+        if self.route_log is not None:
+            self.route_log[:ids.shape[0]].copy_(ids)
+
     def forward(self, ctx, act, act32):
         return self.forward_deferred(ctx, act, act32).materialize(ctx)
 
@@ -215,15 +211,14 @@ class RoutedExperts(FeedForward):
         if (act.shape[0] <= ops.SMALL_ROUTE_TOKENS and act.shape[0] * self.top_k <= ops.SMALL_ROUTE_ASSIGNMENTS
                 and self.num_experts <= 1024):
             ids, weights, p = self.route_and_plan(ctx, act32)
-            if self.on_route is not None:
-                self.on_route(ids)
+            self._tell_route(ids)
         else:
             ids, weights = self.route(ctx, act32)
-            if self.on_route is not None:
-                self.on_route(ids)
+            self._tell_route(ids)
             p = self.plan(ctx, ids)
         y = self.experts(ctx, act, p)
-        return ExpertUpdate(y, weights, p["row_of_assign"])
+        # each token's expert outputs, not yet summed: the norm after this layer adds them in rank order
+        return WeightedRows(y, weights, p["row_of_assign"])
 
 
 class DenseGatedUnit(FeedForward):

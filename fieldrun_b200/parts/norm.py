@@ -9,7 +9,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import VECTOR, TensorNeed, TensorSource
-from .base import Norm, as_tensor, register_part
+from .base import Norm, WeightedRows, as_tensor, register_part
 
 
 class RMSNorm(Norm):
@@ -30,10 +30,9 @@ class RMSNorm(Norm):
     accepts_deferred = True
 
     def forward(self, ctx, x, *, delta=None, rows=None, want32=False, write_back=True):
-        from .feed_forward import ExpertUpdate
         experts = None
-        if isinstance(delta, ExpertUpdate):
-            experts, delta = (delta.y, delta.weights, delta.row_of_assign), None
+        if isinstance(delta, WeightedRows) and delta.top_k <= ops.NORM_MAX_SUMMED_ROWS:
+            experts, delta = (delta.rows, delta.weights, delta.row_map), None      # the kernel sums them as it reads x
         else:
             delta = as_tensor(ctx, delta)
         count = rows.numel() if rows is not None else x.shape[0]

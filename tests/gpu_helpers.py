@@ -94,31 +94,35 @@ def loaded(name: str, dtype: str, max_tokens: int = 2048, num_slots=None):
 # --------------------------------------------------------------------------- schedules of steps, with the experts picked
 
 class RouteRecorder:
-    """Records which experts the engine picks for every token of every step (through the feed-forward's
-    ``on_route`` hook; recorded steps are switched off meanwhile, since a replayed graph calls no hook)."""
+    """Records which experts the engine picks for every token of every step.  Each routed feed-forward copies
+    its picks into a log on the device (``route_log``); the copy is part of a recorded step too, so decode steps
+    keep running from their recordings while the picks are read.  Recordings made before the logs existed are
+    dropped on the way in, those made with them on the way out."""
 
     def __init__(self, lm):
         self.lm = lm
-        self.pending: list[np.ndarray] = []
         self.routes: dict = {}
 
     def __enter__(self):
-        self.was_recording = self.lm.engine.record_steps
-        self.lm.engine.record_steps = False
-        for block in self.lm.model.blocks:
-            block.feed_forward.on_route = lambda ids: self.pending.append(ids.cpu().numpy().copy())
+        import torch
+        engine = self.lm.engine
+        engine._recorded.clear()
+        self.parts = [block.feed_forward for block in self.lm.model.blocks]
+        for part in self.parts:
+            part.route_log = torch.zeros((engine.max_tokens, part.top_k), dtype=torch.int32, device=engine.device)
         return self
 
     def __exit__(self, *exc):
-        self.lm.engine.record_steps = self.was_recording
-        for block in self.lm.model.blocks:
-            block.feed_forward.on_route = None
+        self.lm.engine._recorded.clear()
+        for part in self.parts:
+            part.route_log = None
         return False
 
     def assign(self, rows):
         """``rows``: (request, position) of every token of the step just run, in the step's order."""
-        runs, self.pending = self.pending, []
-        for run, ids in enumerate(runs):
+        logs = {id(part): part.route_log[:len(rows)].cpu().numpy().copy() for part in self.parts}
+        for run, spec in enumerate(self.lm.model.plan.run_order):
+            ids = logs[id(self.lm.model.blocks[spec.layer].feed_forward)]
             for t, (key, position) in enumerate(rows):
                 self.routes.setdefault(key, {}).setdefault(run, {})[position] = ids[t]
 

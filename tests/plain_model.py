@@ -123,14 +123,15 @@ def softmax_rows(scores):
     return e / np.sum(e, axis=-1, keepdims=True)
 
 
-def causal_attention(q, k, v, num_heads, num_kv_heads, head_dim, scale, window=None):
+def causal_attention(q, k, v, num_heads, num_kv_heads, head_dim, scale, window=None, rows=None):
     """Per query head h with kv = h // (nh / nkv): scores = q_h k_kv^T * scale, -1e30 where j > i,
     softmax, times v_kv (src/minimax.rs:141-154).  ``window`` (not in the reference's MiniMax) hides keys
-    with j <= i - window."""
-    T = q.shape[0]
+    with j <= i - window.  ``rows``: compute these query rows only (q then holds just them; k and v hold every
+    position), for sequences too long for the square of scores."""
+    T = k.shape[0]
     rep = num_heads // num_kv_heads
-    out = np.zeros((T, num_heads * head_dim), dtype=q.dtype)
-    i = np.arange(T)[:, None]
+    i = (np.arange(T) if rows is None else np.asarray(rows))[:, None]
+    out = np.zeros((len(i), num_heads * head_dim), dtype=q.dtype)
     j = np.arange(T)[None, :]
     hidden = j > i
     if window is not None:
@@ -146,9 +147,10 @@ def causal_attention(q, k, v, num_heads, num_kv_heads, head_dim, scale, window=N
     return out
 
 
-def attention_layer(a, W, prefix, s, positions):
+def attention_layer(a, W, prefix, s, positions, rows=None):
     """q/k/v projections without bias, full-width q/k RMSNorm, rotary, attention, output projection
-    (src/minimax.rs:135-155).  Linear weights are (out, in) as in the checkpoint."""
+    (src/minimax.rs:135-155).  Linear weights are (out, in) as in the checkpoint.  ``rows``: the output of
+    these positions only."""
     q = a @ W[prefix + "self_attn.q_proj.weight"].T
     k = a @ W[prefix + "self_attn.k_proj.weight"].T
     v = a @ W[prefix + "self_attn.v_proj.weight"].T
@@ -157,7 +159,9 @@ def attention_layer(a, W, prefix, s, positions):
         k = rms_norm(k, W[prefix + "self_attn.k_norm.weight"], s["eps"])     # one RMS over all nkv*hd
     q = rotary(q, s["nh"], s["hd"], s["rotary"], s["theta"], positions)
     k = rotary(k, s["nkv"], s["hd"], s["rotary"], s["theta"], positions)
-    out = causal_attention(q, k, v, s["nh"], s["nkv"], s["hd"], float(s["hd"]) ** -0.5)
+    if rows is not None:
+        q = q[np.asarray(rows)]
+    out = causal_attention(q, k, v, s["nh"], s["nkv"], s["hd"], float(s["hd"]) ** -0.5, rows=rows)
     return out @ W[prefix + "self_attn.o_proj.weight"].T
 
 

@@ -192,3 +192,29 @@ def test_rotary_tables_are_the_reference_angles():
     assert Rotary({"rotary_dim": 0, "theta": 1.0}).tables(10, "cpu") == (None, None)
     with pytest.raises(ValueError, match="even"):
         Rotary({"rotary_dim": 5, "theta": 1.0})
+
+
+def test_rotary_tables_far_out_and_the_references_float32_recipe():
+    """The reference forms the angle in float32: inv[j] = 1 / theta.powf(2j / R) (src/minimax.rs:50) and
+    ang = (pos as f32) * inv[j] (src/minimax.rs:76).  At position 65,535 a float32 angle of the fastest pair is
+    only known to half a unit in its last place (2^-9 rad = 2.0e-3) plus the position times the rounding of inv
+    (65,535 x 3e-8 = 2.0e-3): two float32 routines (another powf, a fused multiply) differ by that much among
+    themselves.  The library's tables are computed in float64 and rounded once, which lies inside that band;
+    this test states the band and that the tables are within it, from the first position to the 65,536th."""
+    import numpy as np
+    from fieldrun_b200.parts.position import Rotary
+    theta, rotary_dim = 5000000.0, 64
+    cos, sin = Rotary({"rotary_dim": rotary_dim, "theta": theta}).tables(65536, "cpu")
+    j = np.arange(rotary_dim // 2, dtype=np.float32)
+    inv = (np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * j / np.float32(rotary_dim))).astype(np.float32)
+    for first, end, band in ((0, 300, 3e-5), (60000, 65536, 6e-3)):
+        pos = np.arange(first, end).astype(np.float32)
+        ang = (pos[:, None] * inv[None, :]).astype(np.float32)               # the product rounded to float32
+        for table, fn in ((cos, np.cos), (sin, np.sin)):
+            diff = np.abs(table[first:end].numpy().astype(np.float64) - fn(ang.astype(np.float64)))
+            assert diff.max() < band, (first, diff.max())
+            if first:
+                assert diff.max() > 1e-4                                  # far out the two recipes do part: by the band, not more
+                assert diff[:, 16:].max() < 2e-5                          # and only in the fast pairs; the slow ones agree
+    exact = np.arange(60000, 65536, dtype=np.float64)[:, None] * (1.0 / theta ** (2.0 * np.arange(32) / rotary_dim))[None, :]
+    assert np.abs(cos[60000:].numpy() - np.cos(exact)).max() < 1e-7       # the tables are the exact angles, rounded once

@@ -16,6 +16,7 @@ class ScriptedEngine:
         self.seqs = {}
         self.steps = []
         self.alloc_log = []
+        self.release_log = []       # (slot, steps run when it was given back)
 
     def new_sequence(self):
         slot = self.free.pop()
@@ -27,6 +28,7 @@ class ScriptedEngine:
         assert slot in self.seqs, "released twice"
         del self.seqs[slot]
         self.free.append(slot)
+        self.release_log.append((slot, len(self.steps)))
 
     def step(self, slots, tokens, want=None):
         assert len(set(slots)) == len(slots)
@@ -187,3 +189,12 @@ def test_top_k_and_top_p_reach_the_pick():
     assert engine.last_limits == ([5, 0], [0.9, 1.0])
     run_batch(engine, [Request((1, 2), 2, temperature=0.7, index=0)])
     assert engine.last_limits == (None, None)                      # nothing to cut: the plain call
+
+
+def test_an_ended_sequence_gives_its_slot_back_at_once():
+    engine = ScriptedEngine()
+    reqs = [Request((1, 2, 3), 5, index=0), Request((4,), 2, index=1), Request((9, 9), 7, index=2)]
+    run_batch(engine, reqs)
+    # slots 0, 1, 2 in the order of the requests; request 1 ends after 2 steps, request 0 after 5, request 2 after 7
+    assert engine.release_log == [(1, 2), (0, 5), (2, 7)]
+    assert engine.seqs == {} and sorted(engine.free) == list(range(8))

@@ -846,3 +846,104 @@ def test_top_k_and_top_p_floor_and_picks(vocab):
             assert kept[got[r]] and (abs(c[got[r]] - uniform[r]) < 1e-5 or abs(c[max(got[r] - 1, 0)] - uniform[r]) < 1e-5), (r, got[r], want_pick)
     # top_k = 1 is the largest logit whatever the uniform number
     assert got[2] == int(np.argmax(logits[2])) and got[11] == int(np.argmax(logits[11]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,interleaved", [(6, 2, 32, 16, False), (3, 3, 20, 20, False),
+                                                                          (8, 1, 128, 64, False), (4, 2, 16, 8, True)])
+def test_q_and_k_norm_per_head(dtype, heads, kv_heads, head_dim, rotary, interleaved):
+    """One statistic per head and one weight vector of the head's size for all heads, then the rotary."""
+    from fieldrun_b200.parts.position import Rotary
+    rng = np.random.default_rng(21)
+    T = 70
+    qw, kw = heads * head_dim, kv_heads * head_dim
+    qkv = (rng.normal(size=(T, qw + 2 * kw)) * rng.uniform(0.2, 3.0, size=(T, 1))).astype(np.float32)
+    wq = (1 + 0.2 * rng.normal(size=head_dim)).astype(np.float32)
+    wk = (1 + 0.2 * rng.normal(size=head_dim)).astype(np.float32)
+    positions = np.arange(T, dtype=np.int32)[::-1].copy()
+    slot_of = np.zeros(T, dtype=np.int32)
+    keys, values, table, free = paged_cache(rng, 1, 4, kv_heads, head_dim, dtype)
+    table[0, 0], table[0, 1] = free.pop(), free.pop()
+    cos, sin = Rotary({"rotary_dim": rotary, "theta": 99.0, "pairing": "interleaved" if interleaved else "half"}).tables(128, DEV)
+    q_out = torch.empty(T, qw, dtype=TORCH[dtype], device=DEV)
+    ops().qkv_prepare(dev(qkv), dev(wq), dev(wk), 1e-4, cos, sin, dev(positions), dev(slot_of), dev(table), q_out, keys,
+                      values, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, rotary_dim=rotary,
+                      interleaved=interleaved, write_cache=True, per_head=True)
+
+    def normed(x, n, w):
+        per = x.astype(np.float64).reshape(T, n, head_dim)
+        return pm.rms_norm(per, w.astype(np.float64), 1e-4).reshape(T, n * head_dim)
+
+    def rotate(x, n):
+        if not interleaved:
+            return pm.rotary(x, n, head_dim, rotary, 99.0, positions)
+        out = x.copy()
+        ang = positions.astype(np.float64)[:, None] * pm.rotary_inverse_frequencies(99.0, rotary, np.float64)[None, :]
+        for h in range(n):
+            a, b = x[:, h * head_dim:h * head_dim + rotary:2], x[:, h * head_dim + 1:h * head_dim + rotary:2]
+            out[:, h * head_dim:h * head_dim + rotary:2] = a * np.cos(ang) - b * np.sin(ang)
+            out[:, h * head_dim + 1:h * head_dim + rotary:2] = b * np.cos(ang) + a * np.sin(ang)
+        return out
+
+    q = rotate(normed(qkv[:, :qw], heads, wq), heads)
+    k = rotate(normed(qkv[:, qw:qw + kw], kv_heads, wk), kv_heads)
+    close(f64(q_out), q, TOL[dtype], "queries normed per head")
+    kc = f64(keys)
+    for t in (0, 5, 69):
+        page = table[0, positions[t] // 64]
+        close(kc[page, :, positions[t] % 64, :].reshape(-1), k[t], TOL[dtype], f"key of token {t}")
+
+
+@pytest.mark.parametrize("kernel", ["attention_decode_mma", "attention_decode_tma"])
+def test_one_token_attention_sized_too_small_says_so_and_reads_nothing_foreign(kernel):
+    """A caller whose max_chunks is smaller than the longest sequence needs: the merge must stay inside the
+    partial results the launch has (here followed by NaN, which a read beyond them would pick up), and the
+    status word must say that keys were left out."""
+    rng = np.random.default_rng(22)
+    heads, kv_heads, head_dim = 4, 2, 64
+    lengths = [100, 600]                                         # the second needs three chunks of 256
+    keys, values, table, free = paged_cache(rng, 2, 16, kv_heads, head_dim, "bfloat16")
+    keys, values = keys * 0.2, values * 0.2
+    for slot, n in enumerate(lengths):
+        for i in range((n + 63) // 64):
+            table[slot, i] = free.pop()
+    positions = np.array([n - 1 for n in lengths], dtype=np.int32)
+    slot_of = np.arange(2, dtype=np.int32)
+    q = dev(rng.normal(size=(2, heads * head_dim)), torch.bfloat16)
+    out = torch.zeros_like(q)
+    chunks = 2                                                   # one too few
+    room_o, room_ml = 2 * heads * chunks * head_dim, 2 * heads * chunks * 2
+    store = torch.full((room_o + room_ml + 4096,), float("nan"), dtype=torch.float32, device=DEV)
+    part_o = store[:room_o].view(2, heads, chunks, head_dim)
+    part_ml = store[room_o + 2048:room_o + 2048 + room_ml].view(2, heads, chunks, 2)
+    extra = {"chunks_per_block": 1} if kernel == "attention_decode_tma" else {}
+    getattr(ops(), kernel)(q, keys, values, dev(table), dev(positions), dev(slot_of), part_o, part_ml, out, num_heads=heads,
+                           num_kv_heads=kv_heads, head_dim=head_dim, scale=head_dim ** -0.5, window=None, max_chunks=chunks,
+                           **extra)
+    with pytest.raises(ops().KernelError, match="more keys than the launch was sized for"):
+        ops().tc_status_check(q.device)
+    ops().tc_status_check(q.device)                              # the word was cleared by the raise
+    assert torch.isfinite(out.float()).all()
+    # the short sequence is whole; the long one is the attention over the keys the launch did cover
+    ref = reference_attention(f64(q), f64(keys), f64(values), table, np.array([99, 511]), slot_of, heads, kv_heads, head_dim,
+                              head_dim ** -0.5, None)
+    close(f64(out), ref, 1e-2, "within the launch's chunks")
+
+
+def test_a_wait_that_runs_out_becomes_an_error_on_the_host():
+    """One block waits on a barrier nothing arrives on, with a limit of 100,000 cycles: it gives up, leaves its
+    code in the status word and returns; the host turns the word into an error, clears it, and the device goes
+    on working."""
+    o = ops()
+    o.tc_status_check(DEV)                                       # clean before
+    waited = o.wait_probe(DEV, limit_cycles=100_000)
+    assert 100_000 < waited < 50_000_000                         # it did wait, and not for long
+    assert int(o.tc_status(DEV).item()) == 99
+    with pytest.raises(o.KernelError, match="wait probe"):
+        o.tc_status_check(DEV)
+    assert int(o.tc_status(DEV).item()) == 0
+    o.tc_status_check(DEV)
+    a = torch.arange(10, device=DEV)
+    assert int((a * 2).sum().item()) == 90                       # the context is as usable as before
+    with pytest.raises(o.KernelError, match="outside"):
+        o.wait_probe(DEV, limit_cycles=10 ** 10)                 # a long wait is refused, not run

@@ -342,7 +342,11 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
     cache, config, engine_mod, parts, weights_mod = lib()
 
     class RunningMean(parts.Mixer):
-        """Row i of a sequence becomes w * mean(rows 0..i): the state is the running sum and the count."""
+        """Row i of a sequence becomes w * mean(rows 0..i): the state is the running sum and the count.  It
+        reads the step's tables on the device only (which token belongs to which sequence and slot), so a
+        decode step of it can be recorded and replayed; it writes its state as a function of what it read."""
+
+        replayable = True
 
         def __init__(self, spec, dtype):
             super().__init__(spec, dtype)
@@ -359,18 +363,18 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
             return cache.CacheNeed(state_shape=(self.width + 1,))
 
         def forward(self, ctx, act, line, writes_cache):
-            out = torch.empty(act.shape, dtype=torch.float32, device=act.device)
-            at = 0
-            for slot, n in zip(ctx.seq_slots, ctx.seq_q_lens):
-                state = line.state[slot]
-                sums = torch.cumsum(act[at:at + n].float(), dim=0) + state[:self.width]
-                counts = state[self.width] + torch.arange(1, n + 1, device=act.device, dtype=torch.float32)
-                out[at:at + n] = sums / counts[:, None] * self.weight
-                if writes_cache:
-                    state[:self.width] = sums[-1]
-                    state[self.width] = counts[-1]
-                at += n
-            return out
+            tokens, width = act.shape[0], self.width
+            x = act.float()
+            seq_of_tok, slot_of_tok = ctx.tok_seq.long(), ctx.tok_slot.long()
+            first_row = ctx.cu_q_len[:-1].long()[seq_of_tok]                     # first row of each token's sequence
+            state = line.state.index_select(0, slot_of_tok)                      # [T, width + 1]
+            running = torch.cat([torch.zeros(1, width, device=x.device), torch.cumsum(x, dim=0)])
+            sums = running[1:] - running[first_row] + state[:, :width]
+            counts = state[:, width] + (torch.arange(tokens, device=x.device) - first_row + 1).float()
+            if writes_cache:
+                last_row = ctx.cu_q_len[1:].long() - 1
+                line.state.index_copy_(0, ctx.seq_slot.long(), torch.cat([sums[last_row], counts[last_row, None]], dim=1))
+            return sums / counts[:, None] * self.weight
 
     parts.register_part("mixer", "running_mean", RunningMean, replace=True)
     norm = lambda name: config.PartSpec("rmsnorm", {"width": HIDDEN, "eps": 1e-5}, {"weight": name})
@@ -395,7 +399,7 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
     model = engine_mod.DecoderModel(plan, "float32")
     assert model.cache_needs()[0].state_shape == (HIDDEN + 1,) and model.cache_needs()[0].kv_heads == 0
     model.load(source(W, "float32"))
-    engine = engine_mod.Engine(model, max_tokens=512, num_slots=2)
+    engine = engine_mod.Engine(model, max_tokens=512, num_slots=5)
 
     def plain(ids):
         x = W["emb"][ids]
@@ -410,13 +414,17 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
         x = x + pm.expert_swiglu(pm.rms_norm(x, W["n4"], 1e-5), W["g2"], W["u2"], W["d2"])
         return pm.rms_norm(x, W["fn"], 1e-5) @ W["head"].T
 
-    requests = [rng.integers(0, VOCAB, size=n) for n in (40, 9, 21)]
-    for start in (0, 2):                                    # two batches through two slots: the state starts at zero again
-        batch = requests[start:start + 2]
+    assert model.replayable and engine.record_steps          # decode steps of this model run from recordings
+    requests = [rng.integers(0, VOCAB, size=n) for n in (40, 9, 21, 30, 17, 26, 12)]
+    for start, size in ((0, 5), (5, 2)):                    # two batches through five slots: the state starts at zero again
+        batch = requests[start:start + size]
         slots = [engine.new_sequence() for _ in batch]
         heads = [len(r) // 2 for r in batch]
         out = f64(engine.step(slots, [r[:h].tolist() for r, h in zip(batch, heads)], [list(range(h)) for h in heads]))
-        rows = [[out[:heads[0]]], [out[heads[0]:]]][:len(batch)]
+        rows, at = [], 0
+        for h in heads:
+            rows.append([out[at:at + h]])
+            at += h
         step = 0
         while True:
             live = [b for b, (r, h) in enumerate(zip(batch, heads)) if h + step < len(r)]
@@ -431,6 +439,137 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
         for r, got in zip(batch, rows):
             close(np.concatenate(got), plain(r), 1e-5, f"toy mixer, request of {len(r)}")
     engine.cache.check()
+    # five live sequences ran in the recording for six (the last one twice), four in the one for four, ...
+    assert engine.steps_replayed > 10 and engine.steps_recorded <= 6
+
+    # the same decode steps from their recordings and run directly: the same bits
+    def decode_rows(record):
+        engine.record_steps = record
+        slots = [engine.new_sequence() for _ in range(3)]
+        engine.step(slots, [requests[b][:6].tolist() for b in range(3)], [[], [], []])
+        got = [f64(engine.step(slots, [[int(requests[b][6 + k])] for b in range(3)])) for k in range(3)]
+        for s in slots:
+            engine.release(s)
+        return np.stack(got)
+
+    np.testing.assert_array_equal(decode_rows(True), decode_rows(False))
+    engine.record_steps = True
+
+
+def test_layers_with_equal_position_arguments_share_one_table():
+    _, config, engine_mod, _, _ = lib()
+    from tiny_configs import CONFIG_B
+    import fieldrun_b200 as fr
+    lm = fr.random_model(CONFIG_B, fr.RandomInit(seed=1), dtype="float32", max_tokens=256)
+    mixers = [block.mixer for block in lm.model.blocks]
+    assert len({m.cos.data_ptr() for m in mixers}) == 1 and len({id(m.position) for m in mixers}) == 1
+    other = fr.random_model({**CONFIG_B, "rope_theta": 12345.0}, fr.RandomInit(seed=1), dtype="float32", max_tokens=256)
+    assert other.model.blocks[0].mixer.cos.data_ptr() != mixers[0].cos.data_ptr()
+    assert not torch.equal(other.model.blocks[0].mixer.cos, mixers[0].cos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_with_a_norm_per_head(dtype):
+    """q and k normed head by head with one weight vector of the head's size (the other form of q/k norm the
+    attention part offers beside the full-width one of this architecture)."""
+    _, config, _, parts, _ = lib()
+    rng = np.random.default_rng(8)
+    hidden, heads, kv_heads, head_dim, rotary = 72, 6, 3, 16, 8
+    spec = attention_spec(config, hidden, heads, kv_heads, head_dim, rotary, True)
+    spec.args["qk_norm"] = "per_head"
+    part = parts.build_part("mixer", spec, TORCH[dtype])
+    weights = attention_weights(rng, hidden, heads, kv_heads, head_dim, False)
+    weights["L.self_attn.q_norm.weight"] = 1 + 0.2 * rng.normal(size=head_dim)
+    weights["L.self_attn.k_norm.weight"] = 1 + 0.2 * rng.normal(size=head_dim)
+    assert {n.name: n.shape for n in part.tensor_needs()}["L.self_attn.q_norm.weight"] == (head_dim,)
+    part.load(source(weights, dtype))
+    stepper = Stepper([part.cache_need()], dtype)
+    part.prepare(stepper.cache.max_tokens, DEV)
+    W = rounded(weights, [k for k in weights if "proj" in k], dtype)
+    n = 70
+    act = rng.normal(size=(n + 1, hidden)).astype(np.float32)
+    if dtype == "bfloat16":
+        act = torch.from_numpy(act).to(torch.bfloat16).float().numpy()
+
+    def plain(a):
+        pos = np.arange(len(a))
+        q, k, v = (a.astype(np.float64) @ W[f"L.self_attn.{x}_proj.weight"].T for x in "qkv")
+        q = pm.rms_norm(q.reshape(len(a), heads, head_dim), W["L.self_attn.q_norm.weight"], 1e-5).reshape(len(a), -1)
+        k = pm.rms_norm(k.reshape(len(a), kv_heads, head_dim), W["L.self_attn.k_norm.weight"], 1e-5).reshape(len(a), -1)
+        q, k = pm.rotary(q, heads, head_dim, rotary, 777.0, pos), pm.rotary(k, kv_heads, head_dim, rotary, 777.0, pos)
+        return pm.causal_attention(q, k, v, heads, kv_heads, head_dim, head_dim ** -0.5) @ W["L.self_attn.o_proj.weight"].T
+
+    ref = plain(act)
+    slot = stepper.cache.alloc()
+    ctx = stepper.context([slot], [n])
+    out = f64(part.forward(ctx, torch.from_numpy(act[:n]).to(DEV).to(TORCH[dtype]), stepper.cache.line(0), True))
+    stepper.cache.end_step([slot], [n])
+    close(out, ref[:n], TOL[dtype], "a prompt")
+    ctx = stepper.context([slot], [1])
+    out = f64(part.forward(ctx, torch.from_numpy(act[n:]).to(DEV).to(TORCH[dtype]), stepper.cache.line(0), True))
+    close(out, ref[n:], TOL[dtype], "one more token")
+
+
+@pytest.mark.parametrize("candidates", [2, 40])
+def test_a_toy_mixer_hands_the_norm_weighted_rows_to_sum(candidates):
+    """The deferred form that a norm sums while it reads the stream is open to any part: here a mixer defined in
+    the test returns, per token, ``candidates`` rows with weights; the norm after it adds them in order (two: in
+    its kernel; forty: more than the kernel takes, so the update is summed first and then added)."""
+    _, config, engine_mod, parts, weights_mod = lib()
+
+    class Blend(parts.Mixer):
+        replayable = True
+
+        def __init__(self, spec, dtype):
+            super().__init__(spec, dtype)
+            self.width, self.count = int(spec.args["width"]), int(spec.args["candidates"])
+
+        def tensor_needs(self):
+            return [weights_mod.TensorNeed(self.name_of("maps"), (self.count * self.width, self.width), weights_mod.MATRIX, "normal"),
+                    weights_mod.TensorNeed(self.name_of("mix"), (self.count,), weights_mod.VECTOR, "normal")]
+
+        def load(self, src):
+            self.maps, self.mix = (src.fetch(n) for n in self.tensor_needs())
+
+        def forward(self, ctx, act, line, writes_cache):
+            tokens = act.shape[0]
+            rows = (act.float() @ self.maps.float().T).view(tokens * self.count, self.width).contiguous()
+            weights = torch.softmax(self.mix, dim=0).expand(tokens, self.count).contiguous()
+            row_map = torch.arange(tokens * self.count, dtype=torch.int32, device=act.device)
+            return parts.WeightedRows(rows, weights, row_map)
+
+    parts.register_part("mixer", "blend", Blend, replace=True)
+    norm = lambda name: config.PartSpec("rmsnorm", {"width": HIDDEN, "eps": 1e-5}, {"weight": name})
+    layer = config.LayerSpec("pre_norm", config.PartSpec("blend", {"width": HIDDEN, "candidates": candidates},
+                                                         {"maps": "b.maps", "mix": "b.mix"}),
+                             config.PartSpec("dense_gated", {"hidden_size": HIDDEN, "width": 32},
+                                             {"w_gate": "g", "w_up": "u", "w_down": "d"}), norm("n1"), norm("n2"))
+    plan = config.ModelPlan("toy-blend", HIDDEN, VOCAB,
+                            config.PartSpec("token_embedding", {"vocab_size": VOCAB, "width": HIDDEN}, {"weight": "emb"}),
+                            (layer,), (config.RunSpec(0, 0),), norm("fn"),
+                            config.PartSpec("vocab_head", {"vocab_size": VOCAB, "width": HIDDEN}, {"weight": "head"}))
+    rng = np.random.default_rng(9)
+    W = {"emb": rng.normal(size=(VOCAB, HIDDEN)), "head": rng.normal(size=(VOCAB, HIDDEN)) * 0.2,
+         "b.maps": rng.normal(size=(candidates * HIDDEN, HIDDEN)) * 0.1, "b.mix": rng.normal(size=candidates),
+         "g": rng.normal(size=(32, HIDDEN)) * 0.2, "u": rng.normal(size=(32, HIDDEN)) * 0.2, "d": rng.normal(size=(HIDDEN, 32)) * 0.2}
+    for n in ("n1", "n2", "fn"):
+        W[n] = 1 + 0.1 * rng.normal(size=HIDDEN)
+    W = {k: np.asarray(v, dtype=np.float32).astype(np.float64) for k, v in W.items()}
+    model = engine_mod.DecoderModel(plan, "float32")
+    model.load(source(W, "float32"))
+    engine = engine_mod.Engine(model, max_tokens=256, num_slots=2)
+    ids = rng.integers(0, VOCAB, size=23)
+    x = W["emb"][ids]
+    a = pm.rms_norm(x, W["n1"], 1e-5)
+    mix = np.exp(W["b.mix"] - W["b.mix"].max())
+    mix /= mix.sum()
+    x = x + sum(mix[c] * (a @ W["b.maps"][c * HIDDEN:(c + 1) * HIDDEN].T) for c in range(candidates))
+    x = x + pm.expert_swiglu(pm.rms_norm(x, W["n2"], 1e-5), W["g"], W["u"], W["d"])
+    ref = pm.rms_norm(x, W["fn"], 1e-5) @ W["head"].T
+    slot = engine.new_sequence()
+    got = f64(engine.step([slot], [ids.tolist()], [list(range(23))]))
+    engine.release(slot)
+    close(got, ref, 1e-5, f"{candidates} weighted rows per token")
 
 
 def test_a_toy_position_encoding_and_a_toy_routed_feed_forward_are_registered_built_and_stepped():

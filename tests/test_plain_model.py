@@ -63,6 +63,16 @@ def test_attention_is_causal_grouped_and_windowed():
     np.testing.assert_allclose(win[8], pm.causal_attention(q[6:], k[6:], v[6:], nh, nkv, hd, hd ** -0.5)[2])
 
 
+def test_attention_of_chosen_rows_is_the_rows_of_the_whole():
+    rng = np.random.default_rng(31)
+    T, nh, nkv, hd = 40, 4, 2, 6
+    q, k, v = rng.normal(size=(T, nh * hd)), rng.normal(size=(T, nkv * hd)), rng.normal(size=(T, nkv * hd))
+    rows = [0, 17, 39]
+    for window in (None, 9):
+        whole = pm.causal_attention(q, k, v, nh, nkv, hd, 0.3, window=window)
+        np.testing.assert_allclose(pm.causal_attention(q[rows], k, v, nh, nkv, hd, 0.3, window=window, rows=rows), whole[rows])
+
+
 def test_router_bias_decides_choice_only_ties_go_low_and_weights_sum_to_one():
     rng = np.random.default_rng(4)
     a2, W = rng.normal(size=(6, 10)), rng.normal(size=(5, 10))
