@@ -70,12 +70,16 @@ NEAR_TIE_MARGIN = {"float32": 1e-6, "bfloat16": 1.5e-3}
 NEAR_TIE_FACTOR = 4.0
 
 
-def assert_close(got, ref, dtype: str, what: str = "", margins=None) -> None:
+# with the engine's expert picks forced on the plain model the comparison is one of continuous functions: tighter
+FORCED_ROUTES_TOLERANCE = 1e-2
+
+
+def assert_close(got, ref, dtype: str, what: str = "", margins=None, tolerance=None) -> None:
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     worst(got, ref)
     per_row = np.abs(got - ref).max(axis=-1) / max(np.abs(ref).max(), 1e-30)
-    limit = np.full(len(per_row), TOLERANCE[dtype])
+    limit = np.full(len(per_row), TOLERANCE[dtype] if tolerance is None else tolerance)
     if margins is not None:
         limit[np.asarray(margins) < NEAR_TIE_MARGIN[dtype]] *= NEAR_TIE_FACTOR
     bad = per_row > limit
@@ -170,7 +174,8 @@ def check_request(name, dtype, ids, logits, routes=None, what=""):
     sizes = pm.sizes_from_config(config)
     hidden, margins, own = pm.hidden_states(config, weights, ids, forced_routes=routes, return_routes=True)
     head = weights["model.embed_tokens.weight"] if sizes["tied"] else weights["lm_head.weight"]
-    assert_close(logits, hidden @ head.astype(np.float64).T, dtype, what)
+    assert_close(logits, hidden @ head.astype(np.float64).T, dtype, what,
+                 tolerance=FORCED_ROUTES_TOLERANCE if dtype == "bfloat16" else None)
     differs = np.sort(own, axis=-1) != np.sort(np.asarray(routes), axis=-1)
     clear = margins > ROUTE_MARGIN
     bad = differs.any(axis=-1) & clear

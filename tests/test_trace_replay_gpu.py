@@ -42,7 +42,7 @@ def rounded(n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "e"])
 def test_three_ways_of_cutting_the_same_requests(tmp_path, name, dtype):
     ids = {i: request_tokens(name, n, 7) for i, n in enumerate(LENGTHS)}
     refs = {i: plain_logits(name, n, 7) for i, n in enumerate(LENGTHS)}
@@ -104,8 +104,11 @@ def test_a_step_that_wants_nothing_writes_no_file_and_a_full_cache_is_an_error(t
              {"step": 1, "entries": [{"id": "x", "tokens": [4], "want": [0]}], "end": ["x"]}]
     out = replay("a", "float32", steps, tmp_path / "o", 64)
     assert list(out) == [1]
-    ref = plain_logits("a", 1, 0)  # only to touch the helper's cache; the check that matters is below
-    assert ref.shape[1] == out[1].shape[1]
+    # the step that wanted nothing still ran its tokens: position 3's logits are those of the four tokens together
+    import plain_model as pm
+    from gpu_helpers import plain_weights
+    config, weights = plain_weights("a")
+    assert_close(out[1], pm.logits_all_positions(config, weights, [1, 2, 3, 4])[3:], "float32", "the token after a silent step")
     text = json.dumps({"step": 0, "entries": [{"id": "y", "tokens": list(range(100)), "want": [99]}], "end": []}) + "\n"
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folder("a"), "--dtype", "float32",
                            "--out", str(tmp_path / "p"), "--max-tokens", "64"], input=text, capture_output=True, text=True, timeout=600)
