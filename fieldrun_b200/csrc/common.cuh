@@ -44,9 +44,15 @@ void frb_set_error(const char* fmt, ...);
 // and its writes are visible.  What the launch hides is the time between one kernel's last block and the next
 // kernel's first instruction, which is most of the cost of the small kernels of a decode step.  In a kernel
 // that was started in the ordinary way both instructions do nothing.
+//
+// A kernel may also do work that does not depend on the kernel before it (loading weights) ahead of
+// wait_for_previous_kernel().  If it reads, ahead of the wait, what a kernel two or more places before it in the
+// stream wrote, then the kernel directly before it must call let_next_kernel_start() only after its own wait.
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void after_previous_kernel() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    let_next_kernel_start();
+    wait_for_previous_kernel();
 }
 
 // The largest grid that is started early: the number of SMs, or FIELDRUN_B200_PDL from the environment

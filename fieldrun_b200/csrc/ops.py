@@ -37,6 +37,7 @@ _SIGNATURES = {
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
     "frb_attention_decode_tma": "pppipipppppiiiifiiip",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
+    "frb_weight_stream": "pippppppiipiiiiiiip",
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
     "frb_router_logits": "ppiiip",
@@ -422,6 +423,34 @@ def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Ten
           _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), int(splits), int(groups))
 
 
+import os as _os
+STREAM_RING_KB = int(_os.environ.get("FIELDRUN_B200_STREAM_RING_KB", "144"))   # shared memory of weight_stream's ring of stages
+STREAM_PIECES = int(_os.environ.get("FIELDRUN_B200_STREAM_PIECES", "24"))     # most pieces of 64 k in a stage
+
+
+def weight_stream_takes(features: int, inner: int, paired: bool) -> bool:
+    """Whether :func:`weight_stream` takes these sizes."""
+    return inner % 64 == 0 and inner > 0 and features > 0 and features % (8 if paired else 16) == 0
+
+
+def weight_stream(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
+                  tile_row0: torch.Tensor, num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int,
+                  tile_rows: int, out: torch.Tensor, *, paired: bool, lists_final: bool = False,
+                  blocks: Optional[int] = None, ring_kb: Optional[int] = None, pieces: int = 0) -> None:
+    """Products of a few rows with bfloat16 weights [E, F or 2F, K] as one stream over the weights per SM: TMA into
+    a ring of stages, ``mma.sync`` from shared memory (tiles of 8, 16 or 32 rows).  ``lists_final``: the lists of
+    tiles were complete before the kernel before this one in the stream began (a dense layer's fixed lists; the
+    experts' second product), so the weights may be asked for before that kernel has ended."""
+    _want(w, torch.bfloat16, "streamed weights")
+    _want(x, torch.bfloat16, "streamed inputs")
+    _want(out, torch.bfloat16 if paired else torch.float32, "streamed outputs")
+    feats = w.shape[1] // 2 if paired else w.shape[1]
+    _call("frb_weight_stream", _ptr(w), w.shape[0], _ptr(x), _ptr(x_rows), _ptr(tile_expert), _ptr(tile_row0),
+          _ptr(num_tiles), _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired),
+          int(lists_final), int(blocks or sm_count(w.device)), int(ring_kb or STREAM_RING_KB), int(pieces or STREAM_PIECES),
+          _ptr(tc_status(w.device)))
+
+
 SMALL_ROUTE_ASSIGNMENTS = 1024
 SMALL_ROUTE_TOKENS = 16       # one token per warp of the one-block kernel: beyond that the separate kernels are faster
 ROUTER_SMALL_TOKENS = 8       # most tokens of a step for router_small
@@ -474,6 +503,8 @@ _WAIT_CODES = {
     3: "expert products: the epilogue waiting for the accumulators",
     4: "one-token attention: waiting for a page's copy",
     5: "one-token attention: a sequence has more keys than the launch was sized for (max_chunks); keys were left out",
+    21: "weight stream: the producer waiting for a free stage",
+    22: "weight stream: a compute warp waiting for a loaded stage",
     11: "prompt attention: the producer waiting for a free key/value stage",
     12: "prompt attention: the query tile's copy",
     13: "prompt attention: the MMA thread waiting for a loaded key/value stage",

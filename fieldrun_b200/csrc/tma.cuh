@@ -60,6 +60,13 @@ __device__ __forceinline__ void load_2d(void* dst, const CUtensorMap* map, int x
         ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// one box of a five-dimensional tensor map, its first element at the given coordinates (innermost first)
+__device__ __forceinline__ void load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -86,6 +93,25 @@ static inline bool map_rows_of_64(CUtensorMap* map, const void* base, uint64_t r
     cuuint32_t box[2] = {64, box_rows};
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A map over row-major bfloat16 weights for the kernel that streams them, sixteen rows at a time.  The sixteen
+// rows are two runs of eight (`half_stride` elements apart: the next eight rows, or the same eight features of
+// the second matrix of a pair); a group of sixteen follows the one before it `group_stride` elements on.  The
+// inner size is cut into pieces of 64 (128 bytes), so that a box lies in shared memory as
+// [piece][run][row of eight][64] with the 128-byte swizzle (chunk c of row r at chunk c ^ r).
+// Coordinates: (0, 0, 0, first piece, group); `pieces` pieces per box.  The inner size is a multiple of 64.
+static inline bool map_rows_in_pieces(CUtensorMap* map, const void* base, uint64_t inner, uint64_t half_stride,
+                                      uint64_t group_stride, uint64_t groups, uint32_t pieces) {
+    EncodeFn fn = encoder();
+    if (!fn) return false;
+    cuuint64_t dims[5] = {64, 8, 2, inner / 64, groups};
+    cuuint64_t strides[4] = {inner * 2, half_stride * 2, 128, group_stride * 2};
+    cuuint32_t box[5] = {64, 8, 2, pieces, 1};
+    cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

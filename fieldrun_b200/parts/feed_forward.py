@@ -152,6 +152,14 @@ class RoutedExperts(FeedForward):
             ops.expert_gemm_tc(self.w2, hidden, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
                                p["max_tiles"], p["tile_rows"], y, paired=False)
             return y
+        if self.streams() and ops.weight_stream_takes(self.expert_width, self.hidden_size, paired=True) \
+                and ops.weight_stream_takes(self.hidden_size, self.expert_width, paired=False):
+            ops.weight_stream(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                              p["max_tiles"], p["tile_rows"], hidden, paired=True)
+            # the second product's lists are the first one's: its weights may be on their way while the first still runs
+            ops.weight_stream(self.w2, hidden, None, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
+                              p["max_tiles"], p["tile_rows"], y, paired=False, lists_final=True)
+            return y
         if self.streams():
             tiles = min(p["rows"], self.num_experts)           # about as many tiles as experts that got rows
             ops.expert_gemm_mma(self.w13, act, p["sorted_token"], p["tile_expert"], p["tile_row0"], p["num_tiles"],

@@ -16,7 +16,7 @@ import torch
 from ..csrc import ops
 
 _ONE_TILE: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]] = {}
-STREAM_ROWS = 32          # up to this many rows a dense product is a stream over the weight (see experts_mma.cu)
+STREAM_ROWS = 32          # up to this many rows a dense product is a stream over the weight (see experts_stream.cu)
 STREAM_FEATURES = 65536   # beyond this many output features the library product is at the memory roofline anyway
 
 
@@ -62,8 +62,13 @@ def linear(rows: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]
         tile_rows = 8 if count <= 8 else 16 if count <= 16 else 32
         tile_expert, tile_row0, num_tiles, offsets = _one_tile(rows.device, count)
         result = out if out is not None else torch.empty((count, features), dtype=torch.float32, device=rows.device)
-        ops.expert_gemm_mma(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
-                            tile_rows, result, paired=False, **ops.stream_shape(1, features, inner, tile_rows))
+        if ops.weight_stream_takes(features, inner, paired=False):
+            # the lists of this one tile never change, so the weights may be on their way before the rows are ready
+            ops.weight_stream(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
+                              tile_rows, result, paired=False, lists_final=True)
+        else:
+            ops.expert_gemm_mma(weight.view(1, features, inner), rows, None, tile_expert, tile_row0, num_tiles, offsets, 1,
+                                tile_rows, result, paired=False, **ops.stream_shape(1, features, inner, tile_rows))
         return result
     with ops.timed(f"library_mm[{features}x{inner}]"):
         result = torch.mm(rows, weight.t(), out_dtype=torch.float32)

@@ -519,6 +519,61 @@ def test_streamed_expert_products(tile_rows, experts, width, hidden, rows_per):
     close(f64(y), ref_y, 2e-5, "streamed down product")
 
 
+@pytest.mark.parametrize("tile_rows,blocks,ring_kb", [(8, None, None), (16, 3, 16), (32, 148, 40), (8, 1, 200)])
+@pytest.mark.parametrize("experts,width,hidden,rows_per", [(4, 64, 192, [0, 1, 33, 70]), (3, 1536, 256, [5, 0, 9]),
+                                                           (6, 32, 3072, [1, 2, 8, 9, 0, 17]), (2, 40, 1600, [3, 12])])
+def test_weight_stream_products(tile_rows, blocks, ring_kb, experts, width, hidden, rows_per):
+    """The persistent stream: inner sizes that are no multiple of a stage (192, 1600), one block taking every item,
+    more blocks than items, rings of one to twelve stages, empty experts, tiles with fewer rows than they hold."""
+    rng = np.random.default_rng(24)
+    w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.1, torch.bfloat16)
+    w2_width = (width + 63) // 64 * 64                       # the second product's inner size must be a multiple of 64
+    w2 = dev(rng.normal(size=(experts, hidden // 16 * 16, w2_width)) * 0.1, torch.bfloat16)
+    tokens = 50
+    x = dev(rng.normal(size=(tokens, hidden)), torch.bfloat16)
+    n = sum(rows_per)
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    sorted_token = rng.integers(0, tokens, size=n).astype(np.int32)
+    tiles = [(e, offsets[e] + r) for e in range(experts) for r in range(0, rows_per[e], tile_rows)]
+    tile_expert = np.array([t[0] for t in tiles] + [0, 0], dtype=np.int32)
+    tile_row0 = np.array([t[1] for t in tiles] + [0, 0], dtype=np.int32)
+    num_tiles = np.array([len(tiles)], dtype=np.int32)
+    hidden_out = torch.full((n, width), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops().weight_stream(w13, x, dev(sorted_token), dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                        len(tiles) + 2, tile_rows, hidden_out, paired=True, blocks=blocks, ring_kb=ring_kb)
+    xs, w13f, w2f = f64(x), f64(w13), f64(w2)
+    expert_of = np.repeat(np.arange(experts), rows_per)
+    ref_h = np.stack([pm.silu(xs[sorted_token[r]] @ w13f[expert_of[r], :width].T) * (xs[sorted_token[r]] @ w13f[expert_of[r], width:].T)
+                      for r in range(n)])
+    close(f64(hidden_out), ref_h, 1e-2, "streamed gate/up product")
+    h2 = dev(rng.normal(size=(n, w2_width)), torch.bfloat16)
+    y = torch.full((n, w2.shape[1]), 9.0, dtype=torch.float32, device=DEV)
+    ops().weight_stream(w2, h2, None, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets),
+                        len(tiles) + 2, tile_rows, y, paired=False, lists_final=True, blocks=blocks, ring_kb=ring_kb)
+    ref_y = np.stack([f64(h2)[r] @ w2f[expert_of[r]].T for r in range(n)])
+    close(f64(y), ref_y, 2e-5, "streamed down product")
+    ops().tc_status_check(DEV)
+
+
+def test_weight_stream_gives_a_row_the_same_bits_whatever_else_the_step_holds():
+    rng = np.random.default_rng(25)
+    experts, width, hidden = 5, 48, 1024
+    w = dev(rng.normal(size=(experts, width, hidden)) * 0.1, torch.bfloat16)
+    x = dev(rng.normal(size=(20, hidden)), torch.bfloat16)
+    i32 = lambda *v: dev(np.array(v, dtype=np.int32))
+    alone = torch.empty(1, width, dtype=torch.float32, device=DEV)
+    ops().weight_stream(w, x[7:8].contiguous(), None, i32(3), i32(0), i32(1), i32(0, 0, 0, 0, 1, 1), 1, 8, alone, paired=False)
+    rows_per = [4, 0, 6, 9, 1]
+    offsets = np.concatenate([[0], np.cumsum(rows_per)]).astype(np.int32)
+    order = np.arange(20, dtype=np.int32)
+    order[[7, 12]] = order[[12, 7]]                           # x[7] becomes the third row of expert 3
+    tiles = [(e, offsets[e] + r) for e in range(experts) for r in range(0, rows_per[e], 8)]
+    together = torch.empty(20, width, dtype=torch.float32, device=DEV)
+    ops().weight_stream(w, x, dev(order), i32(*[t[0] for t in tiles]), i32(*[t[1] for t in tiles]), i32(len(tiles)),
+                        dev(offsets), len(tiles), 8, together, paired=False, blocks=7)
+    assert torch.equal(alone[0], together[12])
+
+
 def test_kernels_refuse_sizes_they_do_not_take():
     from fieldrun_b200.csrc.ops import KernelError
     i32 = lambda *v: dev(np.array(v, dtype=np.int32))
