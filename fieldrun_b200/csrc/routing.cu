@@ -287,9 +287,61 @@ struct SmallRouteParams {
     int* num_tiles;
 };
 
+#define TINY_MAX_ASSIGN 128      // up to this many (token, expert) pairs the lists are made without counting over the experts
+
+// The lists for a handful of assignments (a decode step of a few sequences), with one barrier: every thread
+// finds what it has to write by looking through all assignments in shared memory, n^2 comparisons in all.
+// Assignment a lies behind the assignments of lower experts and the earlier ones of its own expert (the order
+// of the counting sort); the first assignment of an expert writes the expert's tiles.
+__device__ __forceinline__ void plan_tiny(const SmallRouteParams& p, const int* s_ids, int* s_tiles) {
+    const int n = p.num_tokens * p.top_k, tile_rows = p.tile_rows;
+    for (int e = threadIdx.x; e <= p.num_experts; e += blockDim.x) {
+        int before = 0;
+        for (int b = 0; b < n; ++b) before += s_ids[b] < e;
+        p.offsets[e] = before;
+    }
+    // every assignment's place; the first assignment of an expert notes how many tiles the expert has
+    int lower = 0, earlier = 0, same = 0;                     // of assignment threadIdx.x (n <= blockDim.x)
+    const int a = threadIdx.x, e = a < n ? s_ids[a] : 0;
+    if (a < n) {
+        for (int b = 0; b < n; ++b) {
+            const int eb = s_ids[b];
+            lower += eb < e;
+            same += eb == e;
+            earlier += eb == e && b < a;
+        }
+        p.sorted_token[lower + earlier] = a / p.top_k;
+        p.row_of_assign[a] = lower + earlier;
+        s_tiles[a] = earlier == 0 ? (same + tile_rows - 1) / tile_rows : 0;
+    }
+    __syncthreads();
+    if (a < n && earlier == 0) {
+        int tile = 0;                                         // tiles of the experts before this one
+        for (int b = 0; b < n; ++b) tile += s_ids[b] < e ? s_tiles[b] : 0;
+        for (int r = 0; r < same; r += tile_rows, ++tile) {
+            p.tile_expert[tile] = e;
+            p.tile_row0[tile] = lower + r;
+        }
+        if (lower + same == n) p.num_tiles[0] = tile;         // the highest expert in use ends the list
+    }
+}
+
 // The work of one block of SMALL_WARPS warps: every token's choice, then the lists.  sm: dynamic shared memory.
 __device__ __forceinline__ void route_and_plan(const SmallRouteParams& p, float* sm, int* s_ids) {
     const int num_experts = p.num_experts, top_k = p.top_k, tile_rows = p.tile_rows;
+    if (p.num_tokens * top_k <= TINY_MAX_ASSIGN && p.num_tokens <= SMALL_WARPS && top_k <= 32) {
+        // a warp per token picks; the picks go to shared memory as well, for the lists
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (warp < p.num_tokens) {
+            pick_experts(p.logits + (size_t)warp * num_experts, p.bias, num_experts, top_k, p.renormalize, p.routed_scale,
+                         sm + (size_t)warp * 2 * num_experts, sm + (size_t)warp * 2 * num_experts + num_experts,
+                         p.ids + (size_t)warp * top_k, p.weights + (size_t)warp * top_k, lane);
+            if (lane < top_k) s_ids[warp * top_k + lane] = p.ids[warp * top_k + lane];      // written by this warp, above
+        }
+        __syncthreads();
+        plan_tiny(p, s_ids, reinterpret_cast<int*>(sm));      // the picks' scratch is free now
+        return;
+    }
     float* scratch = sm;                                                 // [SMALL_WARPS][2][E]
     int* count = reinterpret_cast<int*>(sm + (size_t)SMALL_WARPS * 2 * num_experts);   // [E]
     int* first = count + num_experts;                                    // [E + 1]
@@ -371,6 +423,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_plan_small_kernel(Smal
 
 #define ROUTER_SMALL_TOKENS 8       // most tokens of a step that the one-launch router takes
 #define ROUTER_SMALL_EXPERTS 2      // experts per block: SMALL_WARPS / 2 warps share one expert's inner size
+#define ROUTER_EARLY 4              // 16-byte loads of the router's weight that a lane sends ahead of the wait (widths to 4096)
 
 // Router logits and everything after them in one launch, for steps of at most 8 tokens.  A block computes
 // the logits of two experts: eight warps each take an eighth of an expert's float32 weight row against
@@ -379,7 +432,6 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_plan_small_kernel(Smal
 __global__ void __launch_bounds__(SMALL_WARPS * 32)
 router_small_kernel(const float* __restrict__ act, const float* __restrict__ router, int width, float* __restrict__ logits,
                     unsigned int* __restrict__ ticket, SmallRouteParams p) {
-    after_previous_kernel();
     extern __shared__ float sm[];
     __shared__ int s_ids[SMALL_MAX_ASSIGN];
     __shared__ float s_part[SMALL_WARPS][ROUTER_SMALL_TOKENS];
@@ -388,15 +440,35 @@ router_small_kernel(const float* __restrict__ act, const float* __restrict__ rou
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e = blockIdx.x * ROUTER_SMALL_EXPERTS + warp / WARPS_PER_EXPERT;
     const int part = warp % WARPS_PER_EXPERT;
+    const int vecs = width / 4;
+    const int per_part = (vecs + WARPS_PER_EXPERT - 1) / WARPS_PER_EXPERT;
+    const int begin = part * per_part, end = min(vecs, begin + per_part);
+    const float4* w = reinterpret_cast<const float4*>(router + (size_t)min(e, p.num_experts - 1) * width);
+    // the router's weight does not wait for the kernel before this one: its first loads go out ahead of the wait
+    let_next_kernel_start();
+    float4 early[ROUTER_EARLY];
+#pragma unroll
+    for (int i = 0; i < ROUTER_EARLY; ++i)
+        if (begin + lane + 32 * i < end) early[i] = __ldg(w + begin + lane + 32 * i);
+    wait_for_previous_kernel();
     float acc[ROUTER_SMALL_TOKENS];
 #pragma unroll
     for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) acc[j] = 0.f;
     if (e < p.num_experts) {
-        const int vecs = width / 4;
-        const int per_part = (vecs + WARPS_PER_EXPERT - 1) / WARPS_PER_EXPERT;
-        const int begin = part * per_part, end = min(vecs, begin + per_part);
-        const float4* w = reinterpret_cast<const float4*>(router + (size_t)e * width);
-        for (int k = begin + lane; k < end; k += 32) {
+#pragma unroll
+        for (int i = 0; i < ROUTER_EARLY; ++i) {
+            const int k = begin + lane + 32 * i;
+            if (k < end) {
+#pragma unroll
+                for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) {
+                    if (j < p.num_tokens) {
+                        const float4 xv = __ldg(reinterpret_cast<const float4*>(act + (size_t)j * width) + k);
+                        acc[j] += xv.x * early[i].x + xv.y * early[i].y + xv.z * early[i].z + xv.w * early[i].w;
+                    }
+                }
+            }
+        }
+        for (int k = begin + lane + 32 * ROUTER_EARLY; k < end; k += 32) {
             const float4 wv = __ldg(w + k);
 #pragma unroll
             for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) {
