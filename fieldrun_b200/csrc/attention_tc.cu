@@ -44,6 +44,33 @@ __device__ __forceinline__ float exp2_fast(float x) {
     return y;
 }
 
+// the largest of three (one instruction on this architecture)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// the hardware's instructions on two float32 values in one 64-bit register
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void halves_of(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pairs(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pairs(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 }  // namespace
 
 struct AttnTcParams {
@@ -67,7 +94,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     // p_full[buffer][page of the step]: that page's probabilities of the buffer's step are in tensor memory
-    __shared__ uint64_t q_full, kv_full[AT_STAGES], kv_empty[AT_STAGES], s_full[2], p_full[2][AT_STEP_PAGES], pv_done[2];
+    __shared__ uint64_t q_full, kv_full[AT_STAGES], kv_empty[AT_STAGES], s_full[2], p_full[2][AT_STEP_PAGES];
     __shared__ uint32_t tmem_slot;
     __shared__ int failed_flag;
     volatile int* failed = &failed_flag;
@@ -101,7 +128,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < AT_STAGES; ++s) { bar_init(&kv_full[s], 1); bar_init(&kv_empty[s], 1); }
         for (int i = 0; i < 2; ++i) {
             bar_init(&s_full[i], 1);
-            bar_init(&pv_done[i], 1);
             for (int h = 0; h < AT_STEP_PAGES; ++h) bar_init(&p_full[i][h], 4);
         }
         failed_flag = 0;
@@ -181,8 +207,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     begun[h] = true;
                 }
                 if (!ok) break;
-                mma_commit(&kv_empty[s]);
-                mma_commit(&pv_done[j & 1]);
+                mma_commit(&kv_empty[s]);              // the step's P V has ended: its stage is free, its O may be read
             }
         }
     } else {
@@ -217,7 +242,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < FRB_PAGE / 16; ++c)
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) top[i & 3] = fmaxf(top[i & 3], __uint_as_float(raw[c][i]));
+                    for (int i = 0; i < 16; i += 2)
+                        top[(i >> 1) & 3] = max3(top[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
                 step_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;     // the scale is positive
             } else {
                 step_max = -INFINITY;
@@ -235,22 +261,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool raise = step_max > m_used + AT_RAISE;   // also true on the first page with a visible key
             if (raise) { corr = exp2f(m_used - step_max); m_used = step_max; }
             const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            // 2^(s * scale - m) for two keys at a time: one multiply-add on the pair, the hardware's exponential on each
+            // (a masked key gives 2^-inf = 0), one addition of the pair into one of four running pairs of sums.  (The
+            // softmax is bound by the instructions it issues: a cubic on the multiply-add pipe for part of the
+            // exponentials, to spare the special-function unit, made the kernel slower.)
+            const uint64_t scale_pair = pair_of(p.scale2, p.scale2), shift_pair = pair_of(-m_sub, -m_sub);
+            uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint32_t packed[FRB_PAGE / 32][16];
 #pragma unroll
             for (int c = 0; c < FRB_PAGE / 16; ++c)
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
-                    // 2^(s * scale - m): one multiply-add and the hardware's exponential (a masked key gives 2^-inf = 0)
-                    const float a = exp2_fast(fmaf(__uint_as_float(raw[c][i]), p.scale2, -m_sub));
-                    const float bb = exp2_fast(fmaf(__uint_as_float(raw[c][i + 1]), p.scale2, -m_sub));
-                    sums[i & 2] += a;
-                    sums[(i & 2) + 1] += bb;
+                    float x0, x1;
+                    halves_of(fma_pairs(pair_of(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale_pair, shift_pair), x0, x1);
+                    const float a = exp2_fast(x0), bb = exp2_fast(x1);
+                    sums[(i >> 1) & 3] = add_pairs(sums[(i >> 1) & 3], pair_of(a, bb));
                     packed[c >> 1][(c & 1) * 8 + (i >> 1)] = pack_bf16x2(a, bb);
                 }
-            l_sum = l_sum * corr + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            float sum_even, sum_odd;
+            halves_of(add_pairs(add_pairs(sums[0], sums[1]), add_pairs(sums[2], sums[3])), sum_even, sum_odd);
+            l_sum = l_sum * corr + (sum_even + sum_odd);
             if (begun && __any_sync(0xffffffffu, raise)) {     // rare: this page's O must follow the new maximum
-                if (!bar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 18); ok = false; }
+                if (!bar_wait(&kv_empty[(j - 1) % AT_STAGES], ((j - 1) / AT_STAGES) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 18); ok = false; }
                 fence_after_sync();
 #pragma unroll 1
                 for (int c = 0; c < HD / 16; ++c) {
@@ -276,8 +308,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // page the last step did not have comes here a step early: it waits for the step before the last first
             // (its own last one), after which the last step's barrier is at most one phase behind.
             const int last = num_steps - 1;
-            if (last > 0 && !bar_wait(&pv_done[(last - 1) & 1], ((last - 1) >> 1) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 19); ok = false; }
-            if (!bar_wait(&pv_done[last & 1], (last >> 1) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 19); ok = false; }
+            if (last > 0 && !bar_wait(&kv_empty[(last - 1) % AT_STAGES], ((last - 1) / AT_STAGES) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 19); ok = false; }
+            if (!bar_wait(&kv_empty[last % AT_STAGES], (last / AT_STAGES) & 1, failed)) { if (ok && lane == 0) atomicExch(p.status, 19); ok = false; }
             fence_after_sync();
         }
         // The two threads of a row tell each other their maximum and sum (the stages of keys and values are free now:
