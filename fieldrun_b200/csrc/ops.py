@@ -508,12 +508,10 @@ _WAIT_CODES = {
     11: "prompt attention: the producer waiting for a free key/value stage",
     12: "prompt attention: the query tile's copy",
     13: "prompt attention: the MMA thread waiting for a loaded key/value stage",
-    14: "prompt attention: the MMA thread waiting for a free score buffer",
     15: "prompt attention: the MMA thread waiting for the probabilities",
     16: "prompt attention: the softmax waiting for the scores",
-    17: "prompt attention: the softmax waiting for the product before last",
-    18: "prompt attention: the correction waiting for the last product",
-    19: "prompt attention: the epilogue waiting for the last product",
+    18: "prompt attention: the correction waiting for the step before",
+    19: "prompt attention: the epilogue waiting for the last steps",
     99: "the wait probe, whose wait is meant to run out",
 }
 

@@ -7,7 +7,8 @@ Each case holds between a few hundred MB and 2 GB on the device (more than the L
 warm-up launches and N timed ones (CUDA events), and prints the time per launch with the traffic or
 arithmetic it stands for.  Cases: ``experts_tc`` (prompt-sized expert products on tcgen05: 64 rows per expert), ``experts_tc_large`` (512 rows
 per expert, as in a step of 16k prompt tokens),
-``experts_stream`` (decode-sized expert products, streamed), ``attention_decode`` (pages by TMA),
+``experts_stream`` (decode-sized expert products: the persistent TMA-fed stream; ``experts_stream_mma``: the kernel that
+loads weights into registers, kept for inner sizes that are no multiple of 64), ``attention_decode`` (pages by TMA),
 ``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
 (mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries; ``attention_prefill_tc_long``: one prompt of 16,384 tokens),
 ``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens),
@@ -84,15 +85,18 @@ def experts(kind: str, launches: int) -> dict:
         if kind.startswith("tc"):
             ops.expert_gemm_tc(w13, x, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True)
             ops.expert_gemm_tc(w2, hidden, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False)
-        else:
+        elif kind == "stream_mma":
             ops.expert_gemm_mma(w13, x, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True,
                                 **ops.stream_shape(tiles, WIDTH, HIDDEN, tile_rows, paired=True))
             ops.expert_gemm_mma(w2, hidden, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False,
                                 **ops.stream_shape(tiles, HIDDEN, WIDTH, tile_rows))
+        else:
+            ops.weight_stream(w13, x, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, hidden, paired=True)
+            ops.weight_stream(w2, hidden, None, tile_expert, tile_row0, num_tiles, offsets, tiles, tile_rows, y, paired=False,
+                              lists_final=True)
 
     ms = _time(launch, launches)
-    if kind.startswith("tc"):
-        ops.tc_status_check(dev)
+    ops.tc_status_check(dev)
     weight_bytes = (w13.numel() + w2.numel()) * 2
     flops = 2 * n * 3 * WIDTH * HIDDEN
     return {"case": f"experts_{kind}", "ms": round(ms, 4), "experts": experts_n, "rows": n,
@@ -258,6 +262,7 @@ CASES = {
     "experts_tc": lambda n: experts("tc", n),
     "experts_tc_large": lambda n: experts("tc_large", n),
     "experts_stream": lambda n: experts("stream", n),
+    "experts_stream_mma": lambda n: experts("stream_mma", n),
     "attention_decode": lambda n: attention("decode", n),
     "attention_decode_mma": lambda n: attention("decode_mma", n),
     "attention_prefill": lambda n: attention("prefill", n),
