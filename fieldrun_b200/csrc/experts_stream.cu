@@ -293,7 +293,10 @@ FRB_API int frb_weight_stream(const void* W, int num_experts, const void* X, con
     FRB_CHECK_ARG(map_rows_in_pieces(&map_w, W, (uint64_t)K, half_stride, group_stride, groups, (uint32_t)p.pieces),
                   "weight stream: cuTensorMapEncodeTiled failed or is not available");
     const int nb = tile_rows / 8;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)2 * WS_COMPUTE_WARPS * nb * 4 * 32 * sizeof(float) + 1024;
+    const size_t beside_ring = (size_t)2 * WS_COMPUTE_WARPS * nb * 4 * 32 * sizeof(float) + 1024;
+    while (p.stages > 2 && (size_t)p.stages * stage_bytes + beside_ring > 226 * 1024) --p.stages;   // what a block may have
+    const size_t smem = (size_t)p.stages * stage_bytes + beside_ring;
+    FRB_CHECK_ARG(smem <= 226 * 1024, "weight stream: two stages of %zu bytes do not fit a block's shared memory", stage_bytes);
     const long long items = (long long)max_tiles * p.groups_per_tile;
     FRB_CHECK_ARG(items < (1ll << 31), "weight stream: %d tiles of %d features exceed the launch", max_tiles, F);
     dim3 grid((unsigned)(items < blocks ? items : blocks));
