@@ -38,6 +38,7 @@ using namespace frb_tma;
 struct DecodeTmaParams {
     DecodeAttnParams a;        // max_chunks: partial results per (sequence, head) = blocks along a sequence
     int chunks_per_block;
+    int early;                 // copies go out before the kernel before this one has ended (0: FIELDRUN_B200_ATTENTION_EARLY=0)
     int* status;
 };
 
@@ -47,7 +48,10 @@ template <int HD>
 __global__ void __launch_bounds__(DT_THREADS, 2)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             DecodeTmaParams params) {
-    after_previous_kernel();
+    // The keys and values of earlier tokens, the page table and the positions do not depend on the kernel before this
+    // one (it writes the queries and the new token's key and value): the copies of every page but the sequence's last
+    // go out before that kernel has ended; the warps that multiply wait for it before they read the queries.
+    let_next_kernel_start();
     const DecodeAttnParams& p = params.a;
     constexpr int STAGE_BYTES = FRB_PAGE * HD * 2;
     constexpr int O_STRIDE = HD + 8;
@@ -90,7 +94,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         if (lane == 0) {
             const int* table = p.page_table + (size_t)slot * p.max_pages + first_page;
             const int rounds = (num_pages + DT_WARPS - 1) / DT_WARPS;
+            const int newest = hi_key / FRB_PAGE - first_page;            // the page that the kernel before this one writes to
+            bool waited = false;
+            if (!params.early) { wait_for_previous_kernel(); waited = true; }
             for (int n = 0; n < rounds && ok; ++n) {
+                if (!waited && DT_WARPS * n + DT_WARPS > newest) { wait_for_previous_kernel(); waited = true; }
                 int rows[DT_WARPS];               // each page's first row in [pages * kv heads] rows of pages
 #pragma unroll
                 for (int w = 0; w < DT_WARPS; ++w)
@@ -116,6 +124,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
         }
     } else {
+        wait_for_previous_kernel();
         const bf16* q_base = p.q + ((size_t)b * p.num_heads + (size_t)kvh * group) * HD;
         const bf16* q0 = g < group ? q_base + (size_t)g * HD : nullptr;
         const bf16* q1 = g + 8 < group ? q_base + (size_t)(g + 8) * HD : nullptr;
@@ -338,15 +347,17 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status;
     params.chunks_per_block = chunks_per_block; params.status = status;
+    static const int early = [] { const char* v = getenv("FIELDRUN_B200_ATTENTION_EARLY"); return !(v && v[0] == '0'); }();
+    params.early = early;
     dim3 grid(parts, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
     const size_t smem = (size_t)DT_STAGES * FRB_PAGE * head_dim * 2 + 1024;
     if (head_dim == 64) {
         cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(attention_decode_tma_kernel<64>, grid, dim3(DT_THREADS), smem, stream, map_k, map_v, params);
+        launch_dependent_resident(early ? 2 : 1, attention_decode_tma_kernel<64>, grid, dim3(DT_THREADS), smem, stream, map_k, map_v, params);
         launch_dependent(attention_decode_tma_merge_kernel<64>, merge_grid, dim3(64), 0, stream, params);
     } else {
         cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(attention_decode_tma_kernel<128>, grid, dim3(DT_THREADS), smem, stream, map_k, map_v, params);
+        launch_dependent_resident(early ? 2 : 1, attention_decode_tma_kernel<128>, grid, dim3(DT_THREADS), smem, stream, map_k, map_v, params);
         launch_dependent(attention_decode_tma_merge_kernel<128>, merge_grid, dim3(128), 0, stream, params);
     }
     FRB_RETURN_LAUNCH("attention_decode_tma");

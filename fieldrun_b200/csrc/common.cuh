@@ -71,9 +71,11 @@ inline long frb_dependent_launch_blocks() {
     return most;
 }
 
-// Starts `kernel`, whose first statement is after_previous_kernel().
+// Starts `kernel`, which orders itself behind the kernel before it with the instructions above, early if its grid
+// has at most `per_sm` blocks for every SM (all of them must be able to be resident at once).
 template <typename... Params, typename... Args>
-inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+inline void launch_dependent_resident(int per_sm, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -83,8 +85,14 @@ inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = (long)grid.x * grid.y * grid.z <= frb_dependent_launch_blocks() ? 1 : 0;
+    config.numAttrs = (long)grid.x * grid.y * grid.z <= per_sm * frb_dependent_launch_blocks() ? 1 : 0;
     cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+
+// Starts `kernel`, whose first statement is after_previous_kernel(), early if its grid has at most a block per SM.
+template <typename... Params, typename... Args>
+inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    launch_dependent_resident(1, kernel, grid, block, smem, stream, args...);
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
