@@ -16,7 +16,9 @@ import torch
 from ..csrc import ops
 
 _ONE_TILE: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]] = {}
-STREAM_ROWS = 32          # up to this many rows a dense product is a stream over the weight (see experts_stream.cu)
+STREAM_ROWS = 8           # up to this many rows a dense product is a stream over the weight (experts_stream.cu); beyond, each
+                          # item's rows of x are as many bytes as its weights and the library's product is faster (measured at
+                          # 12 to 32 rows on a B200: 14 to 25 us against 11 for MiniMax-M2's projections)
 STREAM_FEATURES = 65536   # beyond this many output features the library product is at the memory roofline anyway
 
 
