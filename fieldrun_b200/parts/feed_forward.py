@@ -21,7 +21,13 @@ from .base import FeedForward, WeightedRows, register_part
 from .linear import linear
 
 TILE_ROWS = 32        # rows of one expert that a block of the expert kernels takes
-TENSOR_CORE_ROWS_PER_EXPERT = 12     # above this many rows per expert (on average) a step runs on tcgen05
+# Above this many rows per expert (on average) a step's expert products run on tcgen05: tiles of 32 rows and more
+# read an expert's weights once however its rows are spread, at the speed of the memory.  Measured on a B200 at
+# MiniMax-M2's sizes: the streaming kernel with tiles of 8 rows is as fast while no expert gets more than 8 rows
+# (a decode step of 64 sequences, two rows per expert on average: 1,087 against 1,094 us a layer), but a prompt's
+# tokens crowd on fewer experts, and every tile beyond an expert's first reads its weights again (a prompt of 64
+# tokens: 525 against 419 us a layer, of 256: 1,400 against 617).
+TENSOR_CORE_ROWS_PER_EXPERT = {"decode": 4.0, "prompt": 1.0}
 
 
 class RoutedExperts(FeedForward):
@@ -102,17 +108,17 @@ class RoutedExperts(FeedForward):
         """Whether the tensor-core streaming kernel takes this part's sizes (bfloat16, sizes in steps of 32)."""
         return (self.dtype == torch.bfloat16 and self.hidden_size % 32 == 0 and self.expert_width % 32 == 0)
 
-    def on_tensor_cores(self, assignments: int) -> bool:
+    def on_tensor_cores(self, assignments: int, decode: bool = False) -> bool:
         """Whether the tcgen05 kernel runs the step: bfloat16, sizes in steps of 128, and enough rows per
         expert that the products, not the weights alone, are the work."""
         return (self.dtype == torch.bfloat16 and self.hidden_size % 128 == 0 and self.expert_width % 128 == 0
-                and assignments > TENSOR_CORE_ROWS_PER_EXPERT * self.num_experts)
+                and assignments > TENSOR_CORE_ROWS_PER_EXPERT["decode" if decode else "prompt"] * self.num_experts)
 
-    def tile_rows(self, assignments: int) -> int:
+    def tile_rows(self, assignments: int, decode: bool = False) -> int:
         """Rows of one expert that one block takes: few when experts get few rows each, so that no block
         carries accumulators it does not need; enough that most experts fit one tile when they get many."""
         per_expert = assignments / self.num_experts
-        if self.on_tensor_cores(assignments):
+        if self.on_tensor_cores(assignments, decode):
             return next((t for t in (32, 64, 128, 256) if t >= 1.3 * per_expert), 256)
         if not self.streams():
             return TILE_ROWS
@@ -122,7 +128,7 @@ class RoutedExperts(FeedForward):
         tokens = ids.shape[0]
         n = tokens * self.top_k
         chunks = (n + 1023) // 1024
-        tile_rows = self.tile_rows(n)
+        tile_rows = self.tile_rows(n, ctx.is_decode)
         max_tiles = (n + tile_rows - 1) // tile_rows + min(self.num_experts, n)
         p = {
             "counts": ctx.buffer("experts.counts", (chunks * self.num_experts,), torch.int32),
@@ -144,7 +150,7 @@ class RoutedExperts(FeedForward):
         """y [N, d] float32: the output of its expert for every (token, rank), in expert-sorted order."""
         hidden = ctx.buffer("experts.hidden", (p["rows"], self.expert_width), self.dtype)
         y = ctx.buffer("experts.y", (p["rows"], self.hidden_size), torch.float32)
-        if self.on_tensor_cores(p["rows"]):
+        if self.on_tensor_cores(p["rows"], ctx.is_decode):
             gathered = ctx.buffer("experts.gathered", (p["rows"], self.hidden_size), self.dtype)
             ops.gather_rows(act, p["sorted_token"], gathered)
             ops.expert_gemm_tc(self.w13, gathered, p["tile_expert"], p["tile_row0"], p["num_tiles"], p["offsets"],
@@ -179,7 +185,7 @@ class RoutedExperts(FeedForward):
         """For steps of few tokens: choice and lists in one launch."""
         tokens = act32.shape[0]
         n = tokens * self.top_k
-        tile_rows = self.tile_rows(n)
+        tile_rows = self.tile_rows(n, ctx.is_decode)
         max_tiles = (n + tile_rows - 1) // tile_rows + min(self.num_experts, n)
         ids = ctx.buffer("experts.ids", (tokens, self.top_k), torch.int32)
         weights = ctx.buffer("experts.weights", (tokens, self.top_k), torch.float32)

@@ -23,14 +23,19 @@ def test_streaming_blocks_cut_the_inner_size_more_when_there_are_few_tiles():
     assert one_layer > many >= 2
 
 
-@pytest.mark.parametrize("assignments,experts,expected", [(8, 256, 8), (64, 256, 8), (512, 256, 8), (1536, 256, 16), (3000, 256, 16)])
-def test_streamed_experts_get_tiles_of_few_rows(assignments, experts, expected):
+@pytest.mark.parametrize("assignments,decode,tensor_cores,expected", [
+    (8, True, False, 8), (64, True, False, 8), (512, True, False, 8), (1024, True, False, 8), (1536, True, True, 32),
+    (64, False, False, 8), (256, False, False, 8), (512, False, True, 32), (3000, False, True, 32), (10000, False, True, 64),
+    (131072, False, True, 256)])
+def test_experts_get_tiles_by_the_rows_an_expert_sees(assignments, decode, tensor_cores, expected):
+    """256 experts: decode steps stream with tiles of 8 rows up to 4 rows per expert on average, prompts up to 1
+    (their tokens crowd on fewer experts); beyond, tcgen05 with tiles of 32 rows and more."""
     import torch
     from fieldrun_b200.config import PartSpec
     from fieldrun_b200.parts import build_part
-    spec = PartSpec("routed_experts", {"hidden_size": 128, "num_experts": experts, "top_k": 8, "expert_width": 128,
+    spec = PartSpec("routed_experts", {"hidden_size": 128, "num_experts": 256, "top_k": 8, "expert_width": 128,
                                        "scoring": "sigmoid", "renormalize": True, "routed_scale": 1.0, "use_bias": True},
                     {"router": "r", "bias": "b", "w1": "e.{e}.w1", "w3": "e.{e}.w3", "w2": "e.{e}.w2"})
     part = build_part("feed_forward", spec, torch.bfloat16)
-    assert not part.on_tensor_cores(assignments)
-    assert part.tile_rows(assignments) == expected
+    assert part.on_tensor_cores(assignments, decode) == tensor_cores
+    assert part.tile_rows(assignments, decode) == expected
