@@ -300,6 +300,23 @@ def main() -> int:
                              "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4), "flops": flops,
                              "weight_bytes": prefill_bytes,
                              "hbm_frac": round(prefill_bytes / (prefill_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+        # ---- short prompts: their tokens reach only part of the experts, and what bounds them changes with the length --
+        for length in (64, 256):
+            best = None
+            for attempt in range(3):                                # the first run warms up
+                slot = engine.new_sequence()
+                ids = prompts(1, length)
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                engine.step([slot], ids)
+                stop.record()
+                torch.cuda.synchronize()
+                if attempt:
+                    best = start.elapsed_time(stop) if best is None else min(best, start.elapsed_time(stop))
+                engine.release(slot)
+            result["prefill"][f"ms_{length}_tokens"] = round(best, 3)
+            result["prefill"][f"tok_s_{length}_tokens"] = round(length * 1000.0 / best, 1)
         # ---- decode at batch 1 and 64, and every batch size again in mid-run ------------------------------------
         points = {f"decode_b{args.batch}": round(value, 2), f"decode_b{args.batch}_frac": round(achieved / peak["hbm_gbs"], 4),
                   f"decode_b{args.batch}_gbs": round(achieved, 1), f"decode_b{args.batch}_bytes": step_bytes,
