@@ -31,7 +31,7 @@ _SIGNATURES = {
     "frb_expert_combine": "pppiiip",
     "frb_expert_gemm_generic": "ppipppppipiiii",
     "frb_sample_rows": "piipppp",
-    "frb_sample_floor": "piipppp",
+    "frb_sample_floor": "piippppppp",
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifiip",
     "frb_attention_prefill_mma": "ppppippipppppiiifi",
@@ -106,7 +106,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
+_KERNELS_PER_CALL = {"frb_sample_floor": 3, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
 
 
 def launches() -> int:
@@ -315,6 +315,9 @@ def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], unifo
     _call("frb_sample_rows", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(uniform), _ptr(floor), _ptr(out))
 
 
+_FLOOR_SCRATCH: dict[str, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+
 def sample_floor(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
                  floor: torch.Tensor) -> None:
     """floor[r] = the smallest logit of row r that stays when only the ``top_k[r]`` largest logits (0: all) and the
@@ -327,7 +330,16 @@ def sample_floor(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optiona
     if top_p is not None:
         _want(top_p, torch.float32, "top_p")
     rows, vocab = logits.shape
-    _call("frb_sample_floor", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(floor))
+    scratch = _FLOOR_SCRATCH.get(str(logits.device))
+    if scratch is None or scratch[0].numel() < rows:
+        # zero before a call, left zero by it: the rows' largest logits (as ordered keys) and first histograms
+        held = max(rows, 64)
+        scratch = (torch.zeros(held, dtype=torch.int32, device=logits.device),
+                   torch.zeros(held * 256, dtype=torch.int32, device=logits.device),
+                   torch.zeros(held * 256, dtype=torch.int64, device=logits.device))
+        _FLOOR_SCRATCH[str(logits.device)] = scratch
+    _call("frb_sample_floor", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(floor),
+          _ptr(scratch[0]), _ptr(scratch[1]), _ptr(scratch[2]))
 
 
 def gated_unit(both: torch.Tensor, out: torch.Tensor) -> None:

@@ -864,7 +864,7 @@ def test_router_logits_in_float32(tokens, experts, width):
     close(f64(logits), act.astype(np.float64) @ router.astype(np.float64).T, 2e-6, "router logits")
 
 
-@pytest.mark.parametrize("vocab", [37, 1000, 50001])
+@pytest.mark.parametrize("vocab", [37, 1000, 50001, 200064])
 def test_top_k_and_top_p_floor_and_picks(vocab):
     rng = np.random.default_rng(40)
     rows = 12
@@ -876,6 +876,9 @@ def test_top_k_and_top_p_floor_and_picks(vocab):
     uniform = rng.random(size=rows).astype(np.float32)
     floor = torch.full((rows,), 7.0, dtype=torch.float32, device=DEV)
     ops().sample_floor(dev(logits), dev(temperature), dev(top_k), dev(top_p), floor)
+    again = torch.full((rows,), 7.0, dtype=torch.float32, device=DEV)      # the call leaves its scratch as it found it
+    ops().sample_floor(dev(logits), dev(temperature), dev(top_k), dev(top_p), again)
+    assert torch.equal(floor, again)
     picks = torch.empty(rows, dtype=torch.int32, device=DEV)
     ops().sample_rows(dev(logits), dev(temperature), dev(uniform), picks, floor)
     got_floor, got = floor.cpu().numpy(), picks.tolist()
