@@ -93,6 +93,10 @@ weight_stream_kernel(const __grid_constant__ CUtensorMap map_w, StreamParams p) 
             if (!p.lists_final) { wait_for_previous_kernel(); let_next_kernel_start(); waited = true; }
             const long long total = (long long)p.num_tiles[0] * p.groups_per_tile;
             const int begin = (int)(total * blockIdx.x / gridDim.x), end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+            // A step reads every weight once, so the lines of this stream are the first that L2 gives up again
+            // (measured in a decode step of 16 layers: 1.79 -> 1.74 ms at batch 1, 5.06 -> 4.98 ms at batch 8).
+            uint64_t leave_first = 0;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(leave_first));
             int s = 0, issued = 0;                         // the ring's next stage; stages asked for so far
             uint32_t parity = 0;                           // of the phase in which the stage's earlier use was given back
             int tile = begin / p.groups_per_tile, group = begin - tile * p.groups_per_tile;
@@ -109,7 +113,7 @@ weight_stream_kernel(const __grid_constant__ CUtensorMap map_w, StreamParams p) 
                         if (!bar_wait(&empty_bar[s], parity, failed)) { atomicExch(p.status, 21); ok = false; break; }
                     }
                     bar_expect(&full_bar[s], stage_bytes);
-                    load_5d(ring + (size_t)s * stage_bytes, &map_w, 0, 0, 0, st * p.pieces, coordinate, &full_bar[s]);
+                    load_5d_hint(ring + (size_t)s * stage_bytes, &map_w, 0, 0, 0, st * p.pieces, coordinate, &full_bar[s], leave_first);
                     ++issued;
                     if (++s == p.stages) { s = 0; if (issued > p.stages) parity ^= 1; }
                 }
