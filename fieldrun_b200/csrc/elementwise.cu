@@ -90,7 +90,19 @@ __global__ void __launch_bounds__(NORM_BLOCK)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum experts, const int* __restrict__ rows,
                const WT* __restrict__ weight, float eps, int width, OutT* __restrict__ out, float* __restrict__ out32,
                int write_back) {
-    after_previous_kernel();
+    // The norm's weight is nobody's output: it is loaded before the kernel before this one has ended.
+    constexpr int EARLY = 2;                                   // groups of four weights a thread holds in registers
+    const bool early = VEC && width <= 4 * EARLY * NORM_BLOCK;
+    float4 w_early[EARLY];
+    let_next_kernel_start();
+    if (early) {
+#pragma unroll
+        for (int u = 0; u < EARLY; ++u) {
+            const int i = 4 * (u * NORM_BLOCK + threadIdx.x);
+            if (i < width) w_early[u] = load4<WT>(weight + i);
+        }
+    }
+    wait_for_previous_kernel();
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     __shared__ float expert_weight[NORM_MAX_TOP_K];
@@ -152,7 +164,19 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, ExpertSum
     }
     ss = block_sum<NORM_BLOCK>(ss, scratch);
     const float rinv = 1.0f / sqrtf(ss / (float)width + eps);
-    if (VEC) {
+    if (early) {
+#pragma unroll
+        for (int u = 0; u < EARLY; ++u) {
+            const int i = 4 * (u * NORM_BLOCK + threadIdx.x);
+            if (i < width) {
+                const float4 v = *reinterpret_cast<const float4*>(row + i);
+                const float4 w = w_early[u];
+                const float4 y = make_float4(v.x * rinv * w.x, v.y * rinv * w.y, v.z * rinv * w.z, v.w * rinv * w.w);
+                store4<OutT>(out + (size_t)r * width + i, y);
+                if (out32) *reinterpret_cast<float4*>(out32 + (size_t)r * width + i) = y;
+            }
+        }
+    } else if (VEC) {
         for (int i = 4 * threadIdx.x; i < width; i += 4 * NORM_BLOCK) {
             const float4 v = *reinterpret_cast<const float4*>(row + i);
             const float4 w = load4<WT>(weight + i);
@@ -215,6 +239,7 @@ struct QkvParams {
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
     int num_tokens, v_tiles;  // v_tiles: blocks beyond the tokens' own write the values, 64 tokens of one kv head each
     int per_head;             // the norm weights are [head_dim] and every head has a statistic of its own
+    int tables_final;         // positions, slots and page table were complete before the kernel before this one began
 };
 
 #define QKV_BATCH 8          // elements a thread loads before it uses any of them
@@ -326,12 +351,27 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
 // half-split pairing, so that a group's partners are a group too) and rows that start on 16 bytes.
 template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p) {
-    after_previous_kernel();
+    let_next_kernel_start();
     extern __shared__ __align__(16) float raw[];   // Q row, K row, V row; then cos and sin [rotary_dim / 2]
     __shared__ float scratch[32];
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
     const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    int pos_early = 0, slot_early = 0, page_early = -1;
+    if (p.tables_final && blockIdx.x < p.num_tokens) {
+        // positions, slots, pages and angles were there before the kernel before this one began
+        pos_early = p.tok_pos[blockIdx.x];
+        slot_early = p.tok_slot[blockIdx.x];
+        const int table_row = pos_early < p.table_positions ? pos_early : p.table_positions - 1;
+        float* s_cos = raw + all_width;
+        float* s_sin = s_cos + p.rotary_dim / 2;
+        for (int j = threadIdx.x; j < p.rotary_dim / 2; j += NORM_BLOCK) {
+            s_cos[j] = p.cos_table[(size_t)table_row * (p.rotary_dim / 2) + j];
+            s_sin[j] = p.sin_table[(size_t)table_row * (p.rotary_dim / 2) + j];
+        }
+        page_early = p.write_cache ? p.page_table[(size_t)slot_early * p.max_pages + pos_early / FRB_PAGE] : -1;
+    }
+    wait_for_previous_kernel();
     if (blockIdx.x >= p.num_tokens) {
         // The values of 64 tokens of one kv head: read along the dimensions, written along the tokens, whose
         // places in a transposed page are neighbours whenever their positions are (a prompt's are).
@@ -367,8 +407,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     const WT* qw = (const WT*)p.q_weight;
     const WT* kw = (const WT*)p.k_weight;
 
-    const int pos = p.tok_pos[t];
-    const int slot = p.tok_slot[t];
+    const int pos = p.tables_final ? pos_early : p.tok_pos[t];
+    const int slot = p.tables_final ? slot_early : p.tok_slot[t];
     float ssq = 0.f, ssk = 0.f;
     for (int base = 0; base < row_width; base += 4 * QKV_VEC_BATCH * NORM_BLOCK) {
         float4 v[QKV_VEC_BATCH], w[QKV_VEC_BATCH];
@@ -391,11 +431,12 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         }
     }
     const int table_row = pos < p.table_positions ? pos : p.table_positions - 1;   // positions are checked on the host
-    for (int j = threadIdx.x; j < half; j += NORM_BLOCK) {
-        s_cos[j] = p.cos_table[(size_t)table_row * half + j];
-        s_sin[j] = p.sin_table[(size_t)table_row * half + j];
-    }
-    const int page = p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
+    if (!p.tables_final)
+        for (int j = threadIdx.x; j < half; j += NORM_BLOCK) {
+            s_cos[j] = p.cos_table[(size_t)table_row * half + j];
+            s_sin[j] = p.sin_table[(size_t)table_row * half + j];
+        }
+    const int page = p.tables_final ? page_early : p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
     const int in_page = pos % FRB_PAGE;
     float rinv_q = 1.f, rinv_k = 1.f;
     if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
@@ -448,7 +489,7 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
                             const int* tok_pos, const int* tok_slot, const int* page_table, int max_pages,
                             void* q_out, void* k_pages, void* v_pages, int out_dtype, int num_tokens, int num_heads,
                             int num_kv_heads, int head_dim, int rotary_dim, int interleaved, int write_cache,
-                            int per_head, cudaStream_t stream) {
+                            int per_head, int tables_final, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     FRB_CHECK_ARG(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "qkv_prepare: rotary_dim %d must be even and <= head_dim %d",
                   rotary_dim, head_dim);
@@ -460,6 +501,7 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.rotary_dim = rotary_dim; p.interleaved = interleaved; p.max_pages = max_pages; p.write_cache = write_cache;
     p.table_positions = table_positions;
     p.num_tokens = num_tokens; p.v_tiles = 0; p.per_head = per_head && (q_weight || k_weight);
+    p.tables_final = tables_final;
     // per-head statistics: the squares of the q and k rows and one factor per head beside the rows
     const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim +
                          (p.per_head ? (size_t)(num_heads + num_kv_heads) * (head_dim + 1) : 0)) * sizeof(float);

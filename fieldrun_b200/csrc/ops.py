@@ -22,7 +22,7 @@ _P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlon
 _SIGNATURES = {
     "frb_embed_rows": "ppipiii",
     "frb_rmsnorm": "pppppippifiipipi",
-    "frb_qkv_prepare": "pippifppipppipppiiiiiiiii",
+    "frb_qkv_prepare": "pippifppipppipppiiiiiiiiii",
     "frb_wait_probe": "lpp",
     "frb_add_rows": "ppl",
     "frb_attention_generic": "pppipipppiiiifi",
@@ -233,9 +233,12 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
                 tok_slot: torch.Tensor, page_table: Optional[torch.Tensor], q_out: torch.Tensor,
                 k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], *, num_heads: int,
                 num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, write_cache: bool,
-                per_head: bool = False) -> None:
+                per_head: bool = False, tables_final: bool = False) -> None:
     """Q/K RMSNorm (when weights are given: over the whole row with weights [heads * head_dim], or with
-    ``per_head`` over each head with weights [head_dim]), rotary from the tables, Q out, K/V into their pages."""
+    ``per_head`` over each head with weights [head_dim]), rotary from the tables, Q out, K/V into their pages.
+    ``tables_final``: positions, slots and the page table were complete before the kernel before this one in
+    the stream began (a step's tables, with the projection between them and this call); the kernel then reads
+    them, and the angles, while that kernel still runs."""
     if (q_weight is None) != (k_weight is None):
         raise KernelError("q and k norm weights come together or not at all")
     wdtype = q_weight.dtype if q_weight is not None else torch.float32
@@ -251,7 +254,7 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
     _call("frb_qkv_prepare", _ptr(qkv), _code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _code(wdtype), float(eps),
           _ptr(cos_table), _ptr(sin_table), table_positions, _ptr(tok_pos), _ptr(tok_slot), _ptr(page_table), max_pages,
           _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(out_dtype), qkv.shape[0], num_heads, num_kv_heads, head_dim,
-          rotary_dim, int(interleaved), int(write_cache), int(per_head))
+          rotary_dim, int(interleaved), int(write_cache), int(per_head), int(tables_final))
 
 
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,

@@ -106,7 +106,8 @@ class GQAAttention(Mixer):
                         line.page_table, q, line.keys, line.values, num_heads=self.num_heads,
                         num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=rotary_dim,
                         interleaved=bool(self.position.interleaved) if self.position is not None else False,
-                        write_cache=writes_cache, per_head=self.qk_norm == "per_head")
+                        write_cache=writes_cache, per_head=self.qk_norm == "per_head",
+                        tables_final=True)      # the step's tables were there before the projection above began
         out = ctx.buffer("attention.out", (tokens, self.q_width), self.dtype)
         self.attend(ctx, q, line, out)
         return linear(out, self.w_o)

@@ -112,9 +112,11 @@ def test_qk_norm_rotary_and_cache_write(dtype, heads, kv_heads, head_dim, rotary
     if rotary:
         cos, sin = Rotary({"rotary_dim": rotary, "theta": 1234.5, "pairing": "interleaved" if interleaved else "half"}).tables(256, DEV)
     q_out = torch.empty(T, qw, dtype=TORCH[dtype], device=DEV)
+    tables = dev(positions), dev(slot_of), dev(table)
+    torch.cuda.synchronize()             # the tables are there before any kernel: the long ones may be read early
     ops().qkv_prepare(dev(qkv), dev(wq) if normed else None, dev(wk) if normed else None, 1e-5, cos, sin,
-                      dev(positions), dev(slot_of), dev(table), q_out, keys, values, num_heads=heads,
-                      num_kv_heads=kv_heads, head_dim=head_dim, rotary_dim=rotary, interleaved=interleaved, write_cache=True)
+                      *tables, q_out, keys, values, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim,
+                      rotary_dim=rotary, interleaved=interleaved, write_cache=True, tables_final=many)
     q, k, v = (qkv[:, :qw].astype(np.float64), qkv[:, qw:qw + kw].astype(np.float64), qkv[:, qw + kw:].astype(np.float64))
     if normed:
         q, k = pm.rms_norm(q, wq.astype(np.float64), 1e-5), pm.rms_norm(k, wk.astype(np.float64), 1e-5)
