@@ -516,6 +516,7 @@ _WAIT_CODES = {
     1: "expert products: the producer waiting for a free stage",
     2: "expert products: the MMA thread waiting for a loaded stage",
     3: "expert products: the epilogue waiting for the accumulators",
+    6: "expert products: the MMA thread waiting for the epilogue to have read the accumulators",
     4: "one-token attention: waiting for a page's copy",
     5: "one-token attention: a sequence has more keys than the launch was sized for (max_chunks); keys were left out",
     21: "weight stream: the producer waiting for a free stage",

@@ -658,6 +658,20 @@ def test_streamed_products_with_the_inner_size_cut_in_parts(tile_rows, splits, g
 @pytest.mark.parametrize("experts,width,hidden,rows_per", [(3, 128, 256, [70, 0, 300]), (2, 256, 128, [1, 33]),
                                                            (4, 1536, 3072, [64, 5, 0, 130])])
 def test_expert_products_on_tcgen05(tile_rows, experts, width, hidden, rows_per):
+    check_expert_products_on_tcgen05(tile_rows, experts, width, hidden, rows_per)
+
+
+@pytest.mark.parametrize("tile_rows", [32, 128, 256])
+def test_expert_products_on_tcgen05_with_more_items_than_blocks(tile_rows):
+    """The kernel's blocks stay for the whole launch and take items in turn: here every block gets several, with
+    rings and accumulators that run on from one item to the next."""
+    rng = np.random.default_rng(171)
+    rows_per = [int(r) for r in rng.integers(0, 70, size=96)]
+    rows_per[5] = 300                                                     # one expert with many tiles
+    check_expert_products_on_tcgen05(tile_rows, 96, 512, 512, rows_per)
+
+
+def check_expert_products_on_tcgen05(tile_rows, experts, width, hidden, rows_per):
     rng = np.random.default_rng(17)
     w13 = dev(rng.normal(size=(experts, 2 * width, hidden)) * 0.05, torch.bfloat16)
     w2 = dev(rng.normal(size=(experts, hidden, width)) * 0.05, torch.bfloat16)
@@ -673,14 +687,19 @@ def test_expert_products_on_tcgen05(tile_rows, experts, width, hidden, rows_per)
                          hidden_out, paired=True)
     ops().tc_status_check(DEV)
     xs, w13f, w2f = f64(x), f64(w13), f64(w2)
-    expert_of = np.repeat(np.arange(experts), rows_per)
-    ref_h = np.stack([pm.silu(xs[r] @ w13f[expert_of[r], :width].T) * (xs[r] @ w13f[expert_of[r], width:].T) for r in range(n)])
+    ref_h = np.zeros((n, width))
+    for e in range(experts):                                               # one product per expert: its rows lie together
+        rows = slice(offsets[e], offsets[e + 1])
+        ref_h[rows] = pm.silu(xs[rows] @ w13f[e, :width].T) * (xs[rows] @ w13f[e, width:].T)
     close(f64(hidden_out), ref_h, 1e-2, "tcgen05 gate/up product")
     y = torch.full((n, hidden), 9.0, dtype=torch.float32, device=DEV)
     ops().expert_gemm_tc(w2, hidden_out, dev(tile_expert), dev(tile_row0), dev(num_tiles), dev(offsets), len(tiles) + 2, tile_rows,
                          y, paired=False)
     ops().tc_status_check(DEV)
-    ref_y = np.stack([f64(hidden_out)[r] @ w2f[expert_of[r]].T for r in range(n)])
+    ref_y = np.zeros((n, hidden))
+    for e in range(experts):
+        rows = slice(offsets[e], offsets[e + 1])
+        ref_y[rows] = f64(hidden_out)[rows] @ w2f[e].T
     close(f64(y), ref_y, 2e-5, "tcgen05 down product")
 
 
