@@ -149,7 +149,9 @@ __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_count_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int* __restrict__ counts) {
     extern __shared__ int hist[];
     const int c = blockIdx.x;
+    let_next_kernel_start();
     for (int e = threadIdx.x; e < num_experts; e += PLAN_BLOCK) hist[e] = 0;
+    wait_for_previous_kernel();
     __syncthreads();
     const int begin = c * PLAN_CHUNK, end = min(num_assign, begin + PLAN_CHUNK);
     for (int a = begin + threadIdx.x; a < end; a += PLAN_BLOCK) atomicAdd(&hist[ids[a]], 1);
@@ -163,6 +165,7 @@ plan_count_kernel(const int* __restrict__ ids, int num_assign, int num_experts, 
 __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_scan_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int tile_rows, int* __restrict__ offsets,
                  int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+    after_previous_kernel();
     extern __shared__ int total[];       // [E] totals, then [E + 1] first rows, then [E + 1] first tiles
     int* first = total + num_experts;
     int* first_tile = first + num_experts + 1;
@@ -217,6 +220,7 @@ plan_scan_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int 
 __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_fill_kernel(const int* __restrict__ ids, int num_assign, int num_experts, int top_k, const int* __restrict__ counts,
                  int* __restrict__ sorted_token, int* __restrict__ row_of_assign) {
+    after_previous_kernel();
     extern __shared__ int next_place[];          // [E]
     __shared__ int place[PLAN_CHUNK];            // first the chunk's expert ids (all threads fetch them), then their places
     const int c = blockIdx.x;
@@ -256,11 +260,11 @@ FRB_API int frb_expert_plan(const int* ids, int num_tokens, int top_k, int num_e
     FRB_CHECK_ARG((3 * num_experts + 2) * sizeof(int) <= 48 * 1024, "expert plan: %d experts exceed the kernel's 4095", num_experts);
     const int chunks = (num_assign + PLAN_CHUNK - 1) / PLAN_CHUNK;
     const size_t smem = (size_t)num_experts * sizeof(int);
-    plan_count_kernel<<<chunks, PLAN_BLOCK, smem, stream>>>(ids, num_assign, num_experts, counts);
-    plan_scan_kernel<<<1, PLAN_BLOCK, 3 * smem + 2 * sizeof(int), stream>>>(counts, chunks, num_experts, tile_rows, offsets,
-                                                                          tile_expert, tile_row0, num_tiles);
-    plan_fill_kernel<<<chunks, PLAN_BLOCK, smem, stream>>>(ids, num_assign, num_experts, top_k, counts, sorted_token,
-                                                           row_of_assign);
+    launch_dependent(plan_count_kernel, dim3(chunks), dim3(PLAN_BLOCK), smem, stream, ids, num_assign, num_experts, counts);
+    launch_dependent(plan_scan_kernel, dim3(1), dim3(PLAN_BLOCK), 3 * smem + 2 * sizeof(int), stream, counts, chunks, num_experts,
+                     tile_rows, offsets, tile_expert, tile_row0, num_tiles);
+    launch_dependent(plan_fill_kernel, dim3(chunks), dim3(PLAN_BLOCK), smem, stream, ids, num_assign, num_experts, top_k,
+                     (const int*)counts, sorted_token, row_of_assign);
     FRB_RETURN_LAUNCH("expert_plan");
 }
 
