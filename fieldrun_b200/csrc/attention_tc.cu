@@ -108,6 +108,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr uint32_t TMEM_COLS = 512;
     static_assert(O_COL0 + AT_STEP_PAGES * 128 <= TMEM_COLS && HD <= 128 && AT_STEP_PAGES == 2, "tensor memory layout");
 
+    // The step's tables are not the work of the kernel before this one (it writes queries, keys and values): they
+    // are read, and barriers and tensor memory set up, while that kernel still runs.
+    let_next_kernel_start();
     const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = p.num_heads / p.num_kv_heads, kvh = head / group;
@@ -140,6 +143,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = tmem_slot;
+    wait_for_previous_kernel();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -394,10 +398,10 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
     dim3 grid(num_tiles, num_heads);
     if (head_dim == 128) {
         cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_prefill_tc_kernel<128><<<grid, AT_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+        launch_dependent(attention_prefill_tc_kernel<128>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p);
     } else {
         cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_prefill_tc_kernel<64><<<grid, AT_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+        launch_dependent(attention_prefill_tc_kernel<64>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p);
     }
     FRB_RETURN_LAUNCH("attention_prefill_tc");
 }

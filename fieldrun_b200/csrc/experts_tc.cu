@@ -52,8 +52,8 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     // run side by side read the same rows (which stay in L2) and, where an expert has several tiles, the same
     // weights soon after.  The ring of stages runs on from item to item, so the next item's first tiles arrive
     // while the epilogue still reads this item's accumulators.
+    let_next_kernel_start();
     const int feature_blocks = p.F / BLOCK_FEATS;
-    const int num_items = p.num_tiles[0] * feature_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f_total = PAIRED ? 2 * p.F : p.F;
     const int k_blocks = p.K / TC_KBLOCK;
@@ -75,6 +75,8 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    wait_for_previous_kernel();                                  // barriers and tensor memory were set up while it still ran
+    const int num_items = p.num_tiles[0] * feature_blocks;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -236,7 +238,8 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
 #define FRB_TC_LAUNCH(PAIRED, WIDE, EW, OutT)                                                                              \
     do {                                                                                                                   \
         cudaFuncSetAttribute(expert_gemm_tc_kernel<PAIRED, WIDE, EW, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        expert_gemm_tc_kernel<PAIRED, WIDE, EW, OutT><<<grid, TC_THREADS(EW), smem, stream>>>(map_w, map_x, p);             \
+        launch_dependent_resident(EW == 4 ? 2 : 1, expert_gemm_tc_kernel<PAIRED, WIDE, EW, OutT>, grid, dim3(TC_THREADS(EW)), smem, \
+                                  stream, map_w, map_x, p);                                                                 \
     } while (0)
     if (paired) { if (two_per_sm) FRB_TC_LAUNCH(true, false, 4, bf16); else FRB_TC_LAUNCH(true, false, 8, bf16); }
     else if (wide) { if (two_per_sm) FRB_TC_LAUNCH(false, true, 4, float); else FRB_TC_LAUNCH(false, true, 8, float); }
@@ -247,16 +250,21 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
 
 // out[i, :] = x[rows[i], :]: the rows of a step put in expert-sorted order, so that a tile of an expert's
 // rows is one box of a tensor map.
-__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows, uint4* __restrict__ out, int vec_per_row) {
-    const int i = blockIdx.x;
-    const uint4* src = x + (size_t)rows[i] * vec_per_row;
-    uint4* dst = out + (size_t)i * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows, uint4* __restrict__ out, int num_rows,
+                                   int vec_per_row) {
+    after_previous_kernel();
+    for (int i = blockIdx.x; i < num_rows; i += gridDim.x) {
+        const uint4* src = x + (size_t)rows[i] * vec_per_row;
+        uint4* dst = out + (size_t)i * vec_per_row;
+        for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
+    }
 }
 
 FRB_API int frb_gather_rows_bf16(const void* x, const int* rows, void* out, int num_rows, int width, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     FRB_CHECK_ARG(width % 8 == 0, "gather: a width of %d is not a multiple of 8", width);
-    gather_rows_kernel<<<num_rows, 128, 0, stream>>>((const uint4*)x, rows, (uint4*)out, width / 8);
+    // started early where a block has a row (a short prompt); many rows take every block several
+    launch_dependent(gather_rows_kernel, dim3((unsigned)(num_rows < 65536 ? num_rows : 65536)), dim3(128), 0, stream, (const uint4*)x, rows,
+                     (uint4*)out, num_rows, width / 8);
     FRB_RETURN_LAUNCH("gather_rows");
 }
