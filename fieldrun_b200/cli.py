@@ -76,6 +76,8 @@ def _main(argv: list[str] | None = None) -> int:
     parser.add_argument("--generate", type=int, help="generate M tokens")
     parser.add_argument("--n-eval", type=int, default=500, help="positions to score (default 500)")
     parser.add_argument("--dump", help="write predictions or generated tokens, one id per line")
+    parser.add_argument("--logits-dump", help="write the logits of every position of the prompt (the first --ctx ids): "
+                        "little-endian float32 [positions, vocab], as the reference's option of this name does")
     parser.add_argument("--max-tokens", type=int, default=0, help="cache size in tokens (default: what the run needs)")
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     parser.add_argument("--temperature", type=float, default=0.0, help="0 picks the largest logit")
@@ -108,12 +110,21 @@ def _main(argv: list[str] | None = None) -> int:
     else:
         raise SystemExit("[fieldrun_b200] give --ids <ids.json> or --prompts <prompts.json>")
 
-    if args.generate is not None:
+    if args.logits_dump:
+        need = (len(prompts[0]) + 63) // 64 * 64
+    elif args.generate is not None:
         new = args.generate
         need = sum((len(p) + new + 63) // 64 * 64 for p in prompts[:args.batch])
     else:
         need = min(args.batch, args.n_eval) * ((args.ctx + 64) // 64 * 64)
     lm = fr.load(args.model, dtype=args.dtype, max_tokens=max(args.max_tokens, need, 64), max_batch=args.batch)
+
+    if args.logits_dump:
+        # every position's logits of one sequence run whole (src/main.rs:1146-1156 runs each prefix anew)
+        logits = lm.logits(prompts[0]).cpu().numpy().astype("<f4")
+        logits.tofile(args.logits_dump)
+        print(f"[fieldrun_b200] --logits-dump: {logits.shape[0]} positions x {logits.shape[1]} (f32 LE) -> {args.logits_dump}")
+        return 0
 
     if args.generate is not None:
         if args.eos is None:

@@ -44,6 +44,12 @@ def test_random_generate_score_and_dump(tmp_path):
     want = [pm.greedy_pick(pm.logits_all_positions(config, weights, ids[i - 8:i])[-1]) for i in range(8, 13)]
     assert [int(t) for t in dump.read_text().split()] == want and "top-1" in out
 
+    dump = tmp_path / "logits.f32"
+    out = run("--model", folder, "--ids", str(ids_path), "--ctx", "9", "--dtype", "float32", "--logits-dump", str(dump))
+    got = np.fromfile(dump, dtype="<f4").reshape(9, -1)
+    want = pm.logits_all_positions(config, weights, ids[:9])
+    assert "9 positions" in out and got.shape == want.shape and np.abs(got - want).max() < 2e-5 * np.abs(want).max()
+
     prompts_path = tmp_path / "prompts.json"
     prompts_path.write_text(json.dumps([ids[:5], ids[5:16], ids[16:17]]))
     first = run("--model", folder, "--prompts", str(prompts_path), "--generate", "5", "--temperature", "0.9", "--seed", "4",
