@@ -7,7 +7,8 @@ Prints one JSON line.  A step is one decode step of a batch of --batch sequences
 prompts of 2,048 tokens were run first; `value` is decoded tokens a second with the tokens staying on the
 device, `e2e` the same through the Python entry point with host tokens in and out every step, `e2e_loop`
 whole calls of `generate_batch` (prompts included).  It also times a prefill of one 2,048-token prompt, decode
-steps at batch 1 and 64 (their prompts are run too), all three batch sizes again in mid-run (contexts of 3,072),
+steps at batch 1 and 64 (their prompts are run too; beside the device-stepped figure the same with host tokens in
+and out every step, `_e2e`), all three batch sizes again in mid-run (contexts of 3,072),
 each with the bytes its step has to read and the fraction of the memory roofline, and (`long_cache`) a batch of
 8 sequences of 8,192 to 65,536 tokens: their prompts and decode steps over those caches.  With --gpus above 1
 it says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference cannot
@@ -190,18 +191,31 @@ def main() -> int:
         engine.check()                                   # no kernel of the timed steps gave up on a wait
         return start.elapsed_time(stop) / steps, ops.launches() - before, tokens
 
-    def point(batch, length, steps, warmup=3):
-        """Decode at ``batch`` from prompts of ``length``: tokens a second, bytes a step must read, roofline share."""
+    def point(batch, length, steps, warmup=3, host=False):
+        """Decode at ``batch`` from prompts of ``length``: tokens a second, bytes a step must read, roofline share;
+        with ``host`` also tokens a second through ``Engine.step``/``Engine.pick``, host tokens in and out."""
         slots, first = fill(batch, length)
         lo = engine.cache.length(slots[0]) + warmup
-        ms, _, _ = time_decode(slots, first, steps, warmup)
+        ms, _, tokens = time_decode(slots, first, steps, warmup)
         step_bytes, picked = decode_bytes(slots)
+        got = {}
+        if host:
+            host_tokens = tokens.tolist()
+            for _ in range(warmup):
+                host_tokens = engine.pick(engine.step(slots, [[t] for t in host_tokens]))
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            for _ in range(steps):
+                host_tokens = engine.pick(engine.step(slots, [[t] for t in host_tokens]))
+            torch.cuda.synchronize()
+            got["e2e"] = round(batch * steps / (time.perf_counter() - begin), 2)
         for s in slots:
             engine.release(s)
         gbs = step_bytes / (ms * 1e-3) / 1e9
-        return {"tok_s": round(batch * 1000.0 / ms, 2), "ms": round(ms, 4), "bytes": step_bytes, "gbs": round(gbs, 1),
-                "frac": round(gbs / peak["hbm_gbs"], 4), "experts": round(sum(picked) / max(len(picked), 1), 1),
-                "contexts": f"{lo}..{lo + steps}"}
+        got.update({"tok_s": round(batch * 1000.0 / ms, 2), "ms": round(ms, 4), "bytes": step_bytes, "gbs": round(gbs, 1),
+                    "frac": round(gbs / peak["hbm_gbs"], 4), "experts": round(sum(picked) / max(len(picked), 1), 1),
+                    "contexts": f"{lo}..{lo + steps}"})
+        return got
 
     def decode_bytes(slots):
         """Bytes one decode step has to read: every weight it uses once (the experts actually picked, per
@@ -324,11 +338,12 @@ def main() -> int:
                   f"decode_b{args.batch}_contexts": timed_contexts}
         half = max(8, args.steps // 2)
         for batch, length, tag in [(1, PROMPT, ""), (64, PROMPT, "")] + [(b, MID_RUN, "_mid") for b in (1, args.batch, 64)]:
-            got = point(batch, length, half)
+            got = point(batch, length, half, host=not tag)
             name = f"decode_b{batch}{tag}"
             points[name] = got["tok_s"]
-            for key in ("frac", "gbs", "bytes", "experts", "contexts"):
-                points[f"{name}_{key}"] = got[key]
+            for key in ("frac", "gbs", "bytes", "experts", "contexts", "e2e"):
+                if key in got:
+                    points[f"{name}_{key}"] = got[key]
         result["points"] = points
 
     if not args.skip_loop:
