@@ -27,13 +27,22 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
     if (num_experts <= 32 * PICK_PER_LANE && top_k <= 32) {
         // the lane's candidates stay in registers; NaN scores count as the smallest value
         float mine[PICK_PER_LANE], sc[PICK_PER_LANE];
+        // every load goes out before the first value is used (inside the branches below they went one after the
+        // other, each waiting for L2: 5 to 6 us of a decode step's router)
+        float logit[PICK_PER_LANE], shift[PICK_PER_LANE];
+#pragma unroll
+        for (int i = 0; i < PICK_PER_LANE; ++i) {
+            const int e = min(lane + 32 * i, num_experts - 1);
+            logit[i] = __ldcg(z + e);                                    // read through L2: another block may have written it
+            shift[i] = bias ? __ldg(bias + e) : 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < PICK_PER_LANE; ++i) {
             const int e = lane + 32 * i;
             if (e < num_experts) {
-                const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));   // read through L2: another block may have written it
+                const float s = 1.0f / (1.0f + expf(-logit[i]));
                 sc[i] = s;
-                const float c = bias ? s + bias[e] : s;
+                const float c = bias ? s + shift[i] : s;
                 mine[i] = c == c ? c : -INFINITY;
             } else {
                 sc[i] = 0.f;
