@@ -306,15 +306,7 @@ __global__ void __launch_bounds__(HD) attention_decode_tma_merge_kernel(DecodeTm
     const int last = min(pos / keys_per_block, p.max_chunks - 1), first = min(lo_key / keys_per_block, last);
     if (pos / keys_per_block >= p.max_chunks && d == 0) atomicExch(params.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
-    float top = -INFINITY;
-    for (int c = first; c <= last; ++c) top = fmaxf(top, p.part_ml[(row0 + c) * 2]);
-    float sum = 0.f, acc = 0.f;
-    for (int c = first; c <= last; ++c) {
-        const float f = exp2f(p.part_ml[(row0 + c) * 2] - top);
-        sum += p.part_ml[(row0 + c) * 2 + 1] * f;
-        acc += p.part_o[(row0 + c) * HD + d] * f;
-    }
-    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(acc / sum);
+    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d));
 }
 
 // As frb_attention_decode_mma, for head sizes 64 and 128.  num_pages: pages of the cache group (the tensor

@@ -320,6 +320,44 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
     }
 }
 
+// Element d of the merged output of one (sequence, head) from the partial results first..last (maximum and sum in
+// part_ml, unnormalised output in part_o), first to last.  Eight results at a time, all of their loads asked for
+// before the first is used: in a plain loop over the results each load waited for the one before it, which was most of
+// the merge's time.
+template <int HD>
+__device__ __forceinline__ float merged_element(const float* __restrict__ part_ml, const float* __restrict__ part_o, size_t row0,
+                                                int first, int last, int d) {
+    constexpr int AT_ONCE = 8;
+    float top = -INFINITY, sum = 0.f, acc = 0.f;
+    for (int c0 = first; c0 <= last; c0 += AT_ONCE) {
+        float2 ml[AT_ONCE];
+        float o[AT_ONCE];
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u) {
+            const int c = min(c0 + u, last);
+            ml[u] = *reinterpret_cast<const float2*>(part_ml + (row0 + c) * 2);
+            o[u] = part_o[(row0 + c) * HD + d];
+        }
+        float group_top = top;
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u)
+            if (c0 + u <= last) group_top = fmaxf(group_top, ml[u].x);
+        // what was summed so far follows the new maximum (nothing was summed before the first group)
+        const float keep = top == -INFINITY ? 0.f : exp2f(top - group_top);
+        sum *= keep;
+        acc *= keep;
+        top = group_top;
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u)
+            if (c0 + u <= last) {
+                const float f = exp2f(ml[u].x - top);
+                sum += ml[u].y * f;
+                acc += o[u] * f;
+            }
+    }
+    return acc / sum;
+}
+
 // grid (head, sequence): merges the chunks of one (sequence, head), first chunk to last.
 template <int HD>
 __global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnParams p) {
@@ -332,15 +370,7 @@ __global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnPa
     const int last = min(pos / ATT_CHUNK, p.max_chunks - 1), first = min(lo_key / ATT_CHUNK, last);
     if (pos / ATT_CHUNK >= p.max_chunks && p.status && d == 0) atomicExch(p.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
-    float top = -INFINITY;
-    for (int c = first; c <= last; ++c) top = fmaxf(top, p.part_ml[(row0 + c) * 2]);
-    float sum = 0.f, acc = 0.f;
-    for (int c = first; c <= last; ++c) {
-        const float f = exp2f(p.part_ml[(row0 + c) * 2] - top);
-        sum += p.part_ml[(row0 + c) * 2 + 1] * f;
-        acc += p.part_o[(row0 + c) * HD + d] * f;
-    }
-    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(acc / sum);
+    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d));
 }
 
 // Checks the sizes and launches the one-token kernel and its merge.  `what` names the caller in errors.

@@ -472,13 +472,14 @@ router_small_kernel(const float* __restrict__ act, const float* __restrict__ rou
         for (int i = 0; i < ROUTER_EARLY; ++i) {
             const int k = begin + lane + 32 * i;
             if (k < end) {
+                float4 xv[ROUTER_SMALL_TOKENS];                  // every token's loads go out before the first is used
 #pragma unroll
-                for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j) {
-                    if (j < p.num_tokens) {
-                        const float4 xv = __ldg(reinterpret_cast<const float4*>(act + (size_t)j * width) + k);
-                        acc[j] += xv.x * early[i].x + xv.y * early[i].y + xv.z * early[i].z + xv.w * early[i].w;
-                    }
-                }
+                for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j)
+                    xv[j] = __ldg(reinterpret_cast<const float4*>(act + (size_t)min(j, p.num_tokens - 1) * width) + k);
+#pragma unroll
+                for (int j = 0; j < ROUTER_SMALL_TOKENS; ++j)
+                    if (j < p.num_tokens)
+                        acc[j] += xv[j].x * early[i].x + xv[j].y * early[i].y + xv[j].z * early[i].z + xv[j].w * early[i].w;
             }
         }
         for (int k = begin + lane + 32 * ROUTER_EARLY; k < end; k += 32) {
