@@ -353,7 +353,7 @@ template <typename InT, typename OutT, typename WT, int NORM_BLOCK>
 __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p) {
     let_next_kernel_start();
     extern __shared__ __align__(16) float raw[];   // Q row, K row, V row; then cos and sin [rotary_dim / 2]
-    __shared__ float scratch[32];
+    __shared__ float scratch[64];
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
     const int qk_width = q_width + k_width, all_width = qk_width + k_width;
@@ -439,9 +439,13 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     const int page = p.tables_final ? page_early : p.write_cache ? p.page_table[(size_t)slot * p.max_pages + pos / FRB_PAGE] : -1;
     const int in_page = pos % FRB_PAGE;
     float rinv_q = 1.f, rinv_k = 1.f;
-    if (qw) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
-    if (kw) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
-    __syncthreads();
+    if (qw || kw) {
+        block_sum_pair<NORM_BLOCK>(ssq, ssk, scratch);
+        if (qw) rinv_q = 1.0f / sqrtf(ssq / (float)q_width + p.eps);
+        if (kw) rinv_k = 1.0f / sqrtf(ssk / (float)k_width + p.eps);
+    } else {
+        __syncthreads();
+    }
 
     for (int i = 4 * threadIdx.x; i < qk_width; i += 4 * NORM_BLOCK) {
         const bool is_q = i < q_width;
