@@ -35,6 +35,24 @@ class Workspace:
     def bytes_held(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._store.values())
 
+    def send_ints(self, values: np.ndarray) -> torch.Tensor:
+        """``values`` (int32) on the device, by one asynchronous copy out of a pinned buffer that is kept.  The
+        result is this workspace's buffer of step inputs: it holds until the next call."""
+        count = int(values.shape[0])
+        staged = getattr(self, "_pinned", None)
+        if staged is None or staged.numel() < count:
+            if staged is not None:
+                self._pinned_free.synchronize()
+            staged = self._pinned = torch.empty(max(2 * count, 1024), dtype=torch.int32).pin_memory()
+            self._pinned_free = torch.cuda.Event()
+        else:
+            self._pinned_free.synchronize()                # the copy before this one has left the buffer
+        staged[:count] = torch.from_numpy(values)
+        dev = self.buffer("step.inputs", (count,), torch.int32)
+        dev.copy_(staged[:count], non_blocking=True)
+        self._pinned_free.record()
+        return dev
+
 
 def pack_tables(slots: Sequence[int], starts: Sequence[int], q_lens: Sequence[int]) -> np.ndarray:
     """The step's tables as one int32 array: per token position, slot and sequence; per sequence slot, start
@@ -49,13 +67,30 @@ def pack_tables(slots: Sequence[int], starts: Sequence[int], q_lens: Sequence[in
                            np.asarray(starts, dtype=np.int64), q, cu]).astype(np.int32)
 
 
+# Tiles of these many query rows come to the device with a prompt step's tables (the attention kernels' tile sizes);
+# tiles of another size are made, and sent, when they are first asked for.
+QUERY_TILE_ROWS = (128, 16)
+
+
+def _tiles_of(q_lens: Sequence[int], rows: int) -> tuple[list[int], list[int]]:
+    seqs, firsts = [], []
+    for b, n in enumerate(q_lens):
+        for q0 in range(0, n, rows):
+            seqs.append(b)
+            firsts.append(q0)
+    return seqs, firsts
+
+
 class StepContext:
     def __init__(self, workspace: Workspace, dtype: torch.dtype, slots: Sequence[int], starts: Sequence[int],
-                 q_lens: Sequence[int], *, tables: torch.Tensor | None = None, max_kv_len: int | None = None):
+                 q_lens: Sequence[int], *, tables: torch.Tensor | None = None, max_kv_len: int | None = None,
+                 tokens: np.ndarray | None = None, rows: Sequence[int] | None = None):
         """``tables`` (optional) is a device buffer that already holds, or will hold before the kernels run,
         what :func:`pack_tables` makes for this step; it is used instead of a fresh transfer, so that a
         recorded step can be run again with other positions and slots.  ``max_kv_len`` then bounds the
-        lengths the recorded step may be run with."""
+        lengths the recorded step may be run with.  Without ``tables`` everything the step's kernels need from
+        the host goes to the device in one copy: the tables, the step's ``tokens`` and wanted ``rows`` if given
+        (then ``tokens_dev`` and ``rows_dev``), and a prompt's query tiles."""
         self.workspace = workspace
         self.device = workspace.device
         self.dtype = dtype
@@ -70,9 +105,32 @@ class StepContext:
             self.max_kv_len = max(self.max_kv_len, int(max_kv_len))
         self.is_decode = self.max_q_len == 1 and self.num_tokens == self.num_seqs
         t, b = self.num_tokens, self.num_seqs
+        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        self.tokens_dev = self.rows_dev = None
         if tables is None:
-            # one transfer for all the tables
-            dev = torch.from_numpy(pack_tables(self.seq_slots, self.seq_starts, self.seq_q_lens)).to(self.device)
+            # one transfer for all of it
+            parts = [pack_tables(self.seq_slots, self.seq_starts, self.seq_q_lens)]
+            if tokens is not None:
+                parts.append(np.asarray(tokens, dtype=np.int32))
+            if rows is not None:
+                parts.append(np.asarray(rows, dtype=np.int32))
+            tiles = {}
+            if self.max_q_len > 1:
+                for size in QUERY_TILE_ROWS:
+                    seqs, firsts = _tiles_of(self.seq_q_lens, size)
+                    tiles[size] = len(seqs)
+                    parts.append(np.asarray(seqs + firsts, dtype=np.int32))
+            dev = workspace.send_ints(np.concatenate(parts))
+            at = 3 * t + 4 * b + 1
+            if tokens is not None:
+                self.tokens_dev = dev[at:at + t]
+                at += t
+            if rows is not None and len(rows):
+                self.rows_dev = dev[at:at + len(rows)]
+                at += len(rows)
+            for size, count in tiles.items():
+                self._tiles[size] = (dev[at:at + count], dev[at + count:at + 2 * count])
+                at += 2 * count
         else:
             dev = tables
             if dev.numel() != 3 * t + 4 * b + 1 or dev.dtype != torch.int32:
@@ -86,8 +144,6 @@ class StepContext:
         self.seq_q_len = dev[o + 2 * b:o + 3 * b]
         self.cu_q_len = dev[o + 3 * b:o + 4 * b + 1]
 
-        self._tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
-
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.buffer(name, shape, dtype)
 
@@ -95,11 +151,7 @@ class StepContext:
         """Tiles of ``rows`` consecutive new tokens that never span two sequences: (sequence of each tile,
         first row of each tile among its sequence's new tokens), on the device."""
         if rows not in self._tiles:
-            seqs, firsts = [], []
-            for b, n in enumerate(self.seq_q_lens):
-                for q0 in range(0, n, rows):
-                    seqs.append(b)
-                    firsts.append(q0)
+            seqs, firsts = _tiles_of(self.seq_q_lens, rows)
             both = torch.tensor([seqs, firsts], dtype=torch.int32).to(self.device)
             self._tiles[rows] = (both[0].contiguous(), both[1].contiguous())
         return self._tiles[rows]

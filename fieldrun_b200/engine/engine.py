@@ -171,10 +171,8 @@ class Engine:
             self.cache.end_step(slots, q_lens)
             self.steps_run += 1
             return logits
-        ctx = StepContext(self.workspace, self.model.dtype, slots, starts, q_lens)
-        tokens_dev = torch.from_numpy(flat.astype(np.int32)).to(self.device)
-        rows_dev = torch.tensor(rows, dtype=torch.int32, device=self.device) if rows else None
-        logits = self.model.forward(ctx, self.cache, tokens_dev, rows_dev)
+        ctx = StepContext(self.workspace, self.model.dtype, slots, starts, q_lens, tokens=flat, rows=rows)
+        logits = self.model.forward(ctx, self.cache, ctx.tokens_dev, ctx.rows_dev)
         self.cache.end_step(slots, q_lens)
         self.steps_run += 1
         if ctx.num_tokens > len(slots):
