@@ -206,7 +206,9 @@ FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, con
     const auto on16 = [](const void* ptr) { return ((uintptr_t)ptr & 15) == 0; };
     const bool by_four = width % 4 == 0 && on16(x) && on16(delta) && on16(expert_y) && on16(out) && on16(out32) && on16(weight);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
-        if (num_rows <= NORM_FEW_ROWS) {
+        // with the experts' outputs to sum (nine rows read per token) the wide block is the faster one at any number of
+        // rows: 2,048 rows 72 -> 63 us, 16,384 rows 504 -> 466
+        if (num_rows <= NORM_FEW_ROWS || expert_y) {
             auto kernel = by_four ? rmsnorm_kernel<OutT, WT, 1024, true> : rmsnorm_kernel<OutT, WT, 1024, false>;
             if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             launch_dependent(kernel, dim3(num_rows), dim3(1024), smem, stream, x, delta, experts, rows, (const WT*)weight, eps, width,
@@ -237,9 +239,10 @@ struct QkvParams {
     void* v_pages;            // [pages, nkv, hd, PAGE] OutT: values lie transposed within a page
     float eps;
     int num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, max_pages, write_cache, table_positions;
-    int num_tokens, v_tiles;  // v_tiles: blocks beyond the tokens' own write the values, 64 tokens of one kv head each
+    int num_tokens, v_tiles;  // v_tiles: the grid's first v_tiles blocks write the values, 64 tokens of one kv head each
     int per_head;             // the norm weights are [head_dim] and every head has a statistic of its own
     int tables_final;         // positions, slots and page table were complete before the kernel before this one began
+    unsigned head_dim_inverse;   // ceil(2^32 / head_dim): the high word of n times this is n / head_dim for n < 2^24
 };
 
 #define QKV_BATCH 8          // elements a thread loads before it uses any of them
@@ -358,10 +361,12 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
     const int qk_width = q_width + k_width, all_width = qk_width + k_width;
     int pos_early = 0, slot_early = 0, page_early = -1;
-    if (p.tables_final && blockIdx.x < p.num_tokens) {
+    // the blocks that transpose values come first in the grid: they run longest, and at the grid's end they ran alone
+    const int token_block = (int)blockIdx.x - p.v_tiles;
+    if (p.tables_final && token_block >= 0) {
         // positions, slots, pages and angles were there before the kernel before this one began
-        pos_early = p.tok_pos[blockIdx.x];
-        slot_early = p.tok_slot[blockIdx.x];
+        pos_early = p.tok_pos[token_block];
+        slot_early = p.tok_slot[token_block];
         const int table_row = pos_early < p.table_positions ? pos_early : p.table_positions - 1;
         float* s_cos = raw + all_width;
         float* s_sin = s_cos + p.rotary_dim / 2;
@@ -372,12 +377,12 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         page_early = p.write_cache ? p.page_table[(size_t)slot_early * p.max_pages + pos_early / FRB_PAGE] : -1;
     }
     wait_for_previous_kernel();
-    if (blockIdx.x >= p.num_tokens) {
+    if (token_block < 0) {
         // The values of 64 tokens of one kv head: read along the dimensions, written along the tokens, whose
         // places in a transposed page are neighbours whenever their positions are (a prompt's are).
         __shared__ int s_page[QKV_V_TOKENS], s_place[QKV_V_TOKENS];
         OutT* tile = reinterpret_cast<OutT*>(raw);                       // [hd][QKV_V_TOKENS + 2]
-        const int index = blockIdx.x - p.num_tokens;
+        const int index = blockIdx.x;
         const int h = index % p.num_kv_heads, t0 = (index / p.num_kv_heads) * QKV_V_TOKENS;
         const int count = min(QKV_V_TOKENS, p.num_tokens - t0);
         for (int j = threadIdx.x; j < count; j += NORM_BLOCK) {
@@ -385,20 +390,22 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
             s_page[j] = p.page_table[(size_t)p.tok_slot[t0 + j] * p.max_pages + pos / FRB_PAGE];
             s_place[j] = pos % FRB_PAGE;
         }
-        for (int i = threadIdx.x; i < count * hd; i += NORM_BLOCK) {
-            const int j = i / hd, d = i - j * hd;
+        // a warp reads a token's dimensions, then writes a dimension's tokens: no division per element
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (int j = warp; j < count; j += NORM_BLOCK / 32) {
             const InT* row = (const InT*)p.qkv + (size_t)(t0 + j) * all_width + qk_width + h * hd;
-            tile[d * (QKV_V_TOKENS + 2) + j] = from_f32<OutT>(to_f32<InT>(row[d]));
+            for (int d = lane; d < hd; d += 32) tile[d * (QKV_V_TOKENS + 2) + j] = from_f32<OutT>(to_f32<InT>(row[d]));
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < count * hd; i += NORM_BLOCK) {
-            const int d = i / count, j = i - d * count;
-            const size_t at = (((size_t)s_page[j] * p.num_kv_heads + h) * hd + d) * FRB_PAGE + s_place[j];
-            ((OutT*)p.v_pages)[at] = tile[d * (QKV_V_TOKENS + 2) + j];
+        for (int d = warp; d < hd; d += NORM_BLOCK / 32) {
+            for (int j = lane; j < count; j += 32) {
+                const size_t at = (((size_t)s_page[j] * p.num_kv_heads + h) * hd + d) * FRB_PAGE + s_place[j];
+                ((OutT*)p.v_pages)[at] = tile[d * (QKV_V_TOKENS + 2) + j];
+            }
         }
         return;
     }
-    const int t = blockIdx.x;
+    const int t = token_block;
     const int row_width = p.v_tiles ? qk_width : all_width;               // the values are other blocks' work then
     const int half = p.rotary_dim / 2;
     float* s_cos = raw + all_width;
@@ -452,7 +459,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         const float* base = is_q ? raw : raw + q_width;
         const float rinv = is_q ? rinv_q : rinv_k;
         const int local = is_q ? i : i - q_width;
-        const int head = local / hd, dim = local - head * hd;
+        const int head = (int)__umulhi((unsigned)local, p.head_dim_inverse), dim = local - head * hd;   // local / hd
         float4 a = *reinterpret_cast<const float4*>(base + local);
         a = make_float4(a.x * rinv, a.y * rinv, a.z * rinv, a.w * rinv);
         if (dim < p.rotary_dim) {
@@ -481,7 +488,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     if (page >= 0 && !p.v_tiles) {
         const float* vrow = raw + qk_width;
         for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
-            const int head = i / hd, dim = i - head * hd;
+            const int head = (int)__umulhi((unsigned)i, p.head_dim_inverse), dim = i - head * hd;
             const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
             ((OutT*)p.v_pages)[at] = from_f32<OutT>(vrow[i]);
         }
@@ -506,6 +513,8 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.table_positions = table_positions;
     p.num_tokens = num_tokens; p.v_tiles = 0; p.per_head = per_head && (q_weight || k_weight);
     p.tables_final = tables_final;
+    p.head_dim_inverse = (unsigned)((0x100000000ull + (unsigned)head_dim - 1) / (unsigned)head_dim);
+    FRB_CHECK_ARG((long long)(num_heads + 2 * num_kv_heads) * head_dim < (1 << 24), "qkv_prepare: %d heads of %d", num_heads, head_dim);
     // per-head statistics: the squares of the q and k rows and one factor per head beside the rows
     const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim +
                          (p.per_head ? (size_t)(num_heads + num_kv_heads) * (head_dim + 1) : 0)) * sizeof(float);
@@ -524,12 +533,13 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
         } else if (by_four && write_cache) {
             // many tokens: the values go through blocks of their own (64 tokens of a kv head), which write them
             // along the tokens instead of one two-byte store per token and dimension
-            p.v_tiles = 1;
+
             const size_t tile_bytes = (size_t)head_dim * (QKV_V_TOKENS + 2) * sizeof(OutT);
             const size_t bytes = smem > tile_bytes ? smem : tile_bytes;
             auto kernel = qkv_prepare_vec_kernel<InT, OutT, WT, 256>;
             if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
             const int v_blocks = (num_tokens + QKV_V_TOKENS - 1) / QKV_V_TOKENS * num_kv_heads;
+            p.v_tiles = v_blocks;
             launch_dependent(kernel, dim3(num_tokens + v_blocks), dim3(256), bytes, stream, p);
         } else {
             auto kernel = by_four ? qkv_prepare_vec_kernel<InT, OutT, WT, 256> : qkv_prepare_kernel<InT, OutT, WT, 256>;
