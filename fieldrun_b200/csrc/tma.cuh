@@ -60,14 +60,8 @@ __device__ __forceinline__ void load_2d(void* dst, const CUtensorMap* map, int x
         ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
 }
 
-// one box of a five-dimensional tensor map, its first element at the given coordinates (innermost first)
-__device__ __forceinline__ void load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
-}
-
-// the same copy with a cache policy for L2 (see createpolicy)
+// one box of a five-dimensional tensor map, its first element at the given coordinates (innermost first), with a
+// cache policy for L2 (see createpolicy)
 __device__ __forceinline__ void load_5d_hint(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar,
                                              uint64_t policy) {
     asm volatile(
