@@ -12,7 +12,9 @@ loads weights into registers, kept for inner sizes that are no multiple of 64), 
 ``attention_decode_mma`` (pages loaded into registers), ``attention_prefill``
 (mma.sync tiles of 16 queries), ``attention_prefill_tc`` (tcgen05 tiles of 128 queries; ``attention_prefill_tc_long``: one prompt of 16,384 tokens),
 ``decode_small_kernels`` and ``prefill_small_kernels`` (norms, routing, Q/K/V preparation for 8 and 2,048 tokens),
-``step_decode`` and ``step_prefill`` (two whole layers through the engine, for launch lists; not part of ``all``).
+``step_decode`` and ``step_prefill`` (two whole layers through the engine, for launch lists; not part of ``all``),
+``step_timeline`` (a replayed decode step's kernels with their start and end times, from the profiler that ships with torch;
+not part of ``all``).
 The reference has only wall-clock timers around whole runs (src/main.rs:3896-3906); per-kernel numbers are
 this library's own.
 """
@@ -258,6 +260,56 @@ def whole_step(kind: str, launches: int, batch: int = 8) -> dict:
             "ms_per_step_with_host": round(begin.elapsed_time(end) / launches, 3)}
 
 
+def step_timeline(launches: int, batch: int = 8) -> dict:
+    """Three layers of MiniMax-M2's sizes, `batch` sequences over 2,048-token contexts: the start and end of every kernel
+    of a decode step that is replayed from its recording, as the profiler that ships with torch records them (CUPTI).
+    Kernels that start early overlap; what a kernel costs the step is the time from the end of the kernel before it to
+    its own end, which is printed for the middle layer (the first follows the embedding, the last is followed by the
+    head).  Times under the profiler run a few percent long."""
+    from torch.profiler import ProfilerActivity, profile
+    from . import RandomInit, random_model
+    layers, prompt = 3, 2048
+    config = {"architectures": ["MiniMaxM2ForCausalLM"], "hidden_size": HIDDEN, "num_hidden_layers": layers,
+              "num_attention_heads": HEADS, "num_key_value_heads": KV_HEADS, "head_dim": HEAD_DIM, "rotary_dim": 64,
+              "rope_theta": 5e6, "use_qk_norm": True, "num_local_experts": 256, "num_experts_per_tok": 8,
+              "intermediate_size": WIDTH, "vocab_size": 200064, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    lm = random_model(config, RandomInit(seed=2, bias_std=0.01), dtype="bfloat16", max_tokens=(batch + 1) * (prompt + 128),
+                      num_slots=batch + 1)
+    engine = lm.engine
+    rng = np.random.default_rng(0)
+    slots = [engine.new_sequence() for _ in range(batch)]
+    tokens: list[int] = []
+    for first in range(0, batch, 8):
+        group = slots[first:first + 8]
+        tokens += engine.pick(engine.step(group, [rng.integers(0, 200064, size=prompt).tolist() for _ in group]))
+    on_device = torch.tensor(tokens, dtype=torch.int32, device="cuda")
+    for _ in range(4):                                     # the first of these records the step
+        on_device = engine.pick_on_device(engine.step_on_device(slots, on_device))
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(max(launches, 1)):
+            on_device = engine.pick_on_device(engine.step_on_device(slots, on_device))
+        torch.cuda.synchronize()
+    engine.check()
+    kernels = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+    last_step = [i for i, e in enumerate(kernels) if "embed_rows" in e.name][-1]
+    kernels = kernels[last_step:]
+    zero = kernels[0].time_range.start
+    by_end = sorted(kernels, key=lambda e: e.time_range.end)
+    per_layer = (len(kernels) - 3) // layers               # embedding, head and pick stand outside the layers
+    rows, before = [], None
+    for index, e in enumerate(by_end):
+        end = e.time_range.end - zero
+        if 1 + per_layer < index <= 1 + 2 * per_layer:     # the middle layer, from the kernel after its first norm on
+            rows.append({"kernel": e.name.split("(")[0].replace("void ", "")[:48], "starts_us": round(e.time_range.start - zero, 1),
+                         "ends_us": round(end, 1), "adds_us": round(end - before, 1)})
+        before = end
+    return {"case": "step_timeline", "layers": layers, "batch": batch, "context": prompt,
+            "step_us": round(by_end[-1].time_range.end - zero, 1), "layer_us": round(sum(r["adds_us"] for r in rows), 1),
+            "middle_layer": rows}
+
+
 CASES = {
     "experts_tc": lambda n: experts("tc", n),
     "experts_tc_large": lambda n: experts("tc_large", n),
@@ -270,6 +322,7 @@ CASES = {
     "attention_prefill_tc_long": lambda n: attention("prefill_tc_long", n),
     "step_decode": lambda n, batch=8: whole_step("decode", n, batch),
     "step_prefill": lambda n: whole_step("prefill", n),
+    "step_timeline": lambda n, batch=8: step_timeline(n, batch),
     "decode_small_kernels": lambda n: small_kernels(n, 8),
     "prefill_small_kernels": lambda n: small_kernels(n, 2048),
 }
@@ -279,13 +332,14 @@ def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("case", choices=sorted(CASES) + ["all"])
     parser.add_argument("--launches", type=int, default=5)
-    parser.add_argument("--batch", type=int, default=8, help="sequences of step_decode")
+    parser.add_argument("--batch", type=int, default=8, help="sequences of step_decode and step_timeline")
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("fieldrun_b200.profiling needs a CUDA device")
     torch.manual_seed(0)
     for name in ([c for c in sorted(CASES) if not c.startswith("step_")] if args.case == "all" else [args.case]):
-        print(json.dumps(CASES[name](args.launches, args.batch) if name == "step_decode" else CASES[name](args.launches)))
+        print(json.dumps(CASES[name](args.launches, args.batch) if name in ("step_decode", "step_timeline")
+                         else CASES[name](args.launches)))
     return 0
 
 
