@@ -31,6 +31,7 @@ _SIGNATURES = {
     "frb_expert_combine": "pppiiip",
     "frb_expert_gemm_generic": "ppipppppipiiii",
     "frb_sample_rows": "piipppp",
+    "frb_argmax_rows": "piippp",
     "frb_sample_floor": "piippppppp",
     "frb_gated_unit": "ppiii",
     "frb_attention_decode_mma": "ppppipppppiiiifiip",
@@ -113,7 +114,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_sample_floor": 3, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
+_KERNELS_PER_CALL = {"frb_sample_floor": 3, "frb_argmax_rows": 2, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
 
 
 def launches() -> int:
@@ -322,7 +323,22 @@ def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], unifo
     _want(logits, torch.float32, "logits")
     _want(out, torch.int32, "picked tokens")
     rows, vocab = logits.shape
+    if temperature is None and vocab >= ARGMAX_SLICED_VOCAB:
+        # every row greedy and long: many blocks a row, then a warp among their results
+        key = str(logits.device)
+        scratch = _ARGMAX_SCRATCH.get(key)
+        if scratch is None or scratch[0].numel() < rows * 32:
+            count = max(rows, 64) * 32
+            scratch = (torch.empty(count, dtype=torch.float32, device=logits.device),
+                       torch.empty(count, dtype=torch.int32, device=logits.device))
+            _ARGMAX_SCRATCH[key] = scratch
+        _call("frb_argmax_rows", _ptr(logits), rows, vocab, _ptr(scratch[0]), _ptr(scratch[1]), _ptr(out))
+        return
     _call("frb_sample_rows", _ptr(logits), rows, vocab, _ptr(temperature), _ptr(uniform), _ptr(floor), _ptr(out))
+
+
+ARGMAX_SLICED_VOCAB = 16384     # from this many logits a row on, a greedy pick takes 32 blocks a row
+_ARGMAX_SCRATCH: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 _FLOOR_SCRATCH: dict[str, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}

@@ -97,6 +97,77 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __r
     if (lane == 0) out[row] = pick;
 }
 
+// The largest logit of every row in two launches, for large vocabularies: one block scanning a row of 200,064 logits
+// alone takes 15 us (what one SM can read), 32 blocks a row and a warp to pick among their results 4.
+#define ARGMAX_SLICES 32
+#define ARGMAX_BLOCK 256
+
+// grid (slice, row): the largest logit of a slice of the row, the last index among equal ones
+__global__ void __launch_bounds__(ARGMAX_BLOCK)
+argmax_slices_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ slice_val, int* __restrict__ slice_idx) {
+    after_previous_kernel();
+    __shared__ float s_val[ARGMAX_BLOCK / 32];
+    __shared__ int s_idx[ARGMAX_BLOCK / 32];
+    const int slice = blockIdx.x, row = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* x = logits + (size_t)row * vocab;
+    const int per_slice = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int begin = slice * per_slice, end = min(vocab, begin + per_slice);
+    float best = -INFINITY;
+    int best_i = -1;
+    constexpr int AT_ONCE = 8;                                          // loads on their way at a time
+    int i = begin + threadIdx.x;
+    for (; i + (AT_ONCE - 1) * ARGMAX_BLOCK < end; i += AT_ONCE * ARGMAX_BLOCK) {
+        float v[AT_ONCE];
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u) v[u] = x[i + u * ARGMAX_BLOCK];
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u) keep_larger(best, best_i, v[u], i + u * ARGMAX_BLOCK);
+    }
+    for (; i < end; i += ARGMAX_BLOCK) keep_larger(best, best_i, x[i], i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        keep_larger(best, best_i, ov, oi);
+    }
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < ARGMAX_BLOCK / 32; ++w) keep_larger(best, best_i, s_val[w], s_idx[w]);
+        slice_val[row * ARGMAX_SLICES + slice] = best;
+        slice_idx[row * ARGMAX_SLICES + slice] = best_i;
+    }
+}
+
+// one warp per row picks among the slices' results
+__global__ void __launch_bounds__(32)
+argmax_finish_kernel(const float* __restrict__ slice_val, const int* __restrict__ slice_idx, int* __restrict__ out) {
+    after_previous_kernel();
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float best = slice_val[row * ARGMAX_SLICES + lane];
+    int best_i = slice_idx[row * ARGMAX_SLICES + lane];
+    if (best_i < 0) best = -INFINITY;                                  // a slice of nothing comparable
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        keep_larger(best, best_i, ov, oi);
+    }
+    if (lane == 0) out[row] = best_i < 0 ? 0 : best_i;
+}
+
+// logits [rows, vocab] float32 -> out[r] = the index of row r's largest logit (the last one on ties, 0 if nothing
+// compares).  slice_val, slice_idx: scratch of rows * 32 elements each.
+FRB_API int frb_argmax_rows(const float* logits, int rows, int vocab, float* slice_val, int* slice_idx, int* out,
+                            cudaStream_t stream) {
+    if (rows == 0) return 0;
+    FRB_CHECK_ARG(vocab >= 1 && rows <= 65535, "argmax: %d rows of %d", rows, vocab);
+    launch_dependent_resident(8, argmax_slices_kernel, dim3(ARGMAX_SLICES, rows), dim3(ARGMAX_BLOCK), 0, stream, logits, vocab,
+                              slice_val, slice_idx);
+    launch_dependent(argmax_finish_kernel, dim3(rows), dim3(32), 0, stream, (const float*)slice_val, (const int*)slice_idx, out);
+    FRB_RETURN_LAUNCH("argmax_rows");
+}
+
 // logits [rows, vocab] float32; temperature [rows] (null or <= 0: greedy); uniform [rows] in [0, 1); floor [rows] or
 // null: the smallest logit that may be picked (from frb_sample_floor).
 FRB_API int frb_sample_rows(const float* logits, int rows, int vocab, const float* temperature, const float* uniform,

@@ -324,6 +324,32 @@ def test_gated_unit():
     close(f64(out), pm.silu(both[:, :33].astype(np.float64)) * both[:, 33:], 5e-3, "gated unit")
 
 
+@pytest.mark.parametrize("vocab", [16384, 50001, 200064])
+def test_greedy_picks_over_slices_of_a_long_row(vocab):
+    """Long rows are searched by 32 blocks each: ties inside a slice and across slices go to the last index, values
+    that do not compare are passed over, a row of nothing comparable gives token 0."""
+    rng = np.random.default_rng(101)
+    rows = 9
+    logits = rng.normal(size=(rows, vocab)).astype(np.float32)
+    logits[0, [3, 4]] = 9.0                                                # a tie inside the first slice
+    logits[1, [7, vocab // 2, vocab - 1]] = 9.0                            # across slices
+    logits[2, vocab - 1] = 9.0
+    logits[3, 0] = 9.0
+    logits[4, :] = np.nan
+    logits[5, ::2] = np.nan
+    logits[6, :] = -np.inf
+    logits[6, 1234] = -1e30
+    logits[7, :] = 2.5                                                     # every logit equal: the last one
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample_rows(dev(logits), None, None, out)
+    got = out.tolist()
+    assert got[:4] == [4, vocab - 1, vocab - 1, 0] and got[4] == 0 and got[6] == 1234 and got[7] == vocab - 1
+    assert got[5] == int(np.nanargmax(logits[5])) and got[8] == pm.greedy_pick(logits[8])
+    small = torch.empty(rows, dtype=torch.int32, device=DEV)              # the one-block kernel agrees
+    ops().sample_rows(dev(logits), dev(np.zeros(rows, dtype=np.float32)), dev(np.zeros(rows, dtype=np.float32)), small)
+    assert small.tolist() == got
+
+
 @pytest.mark.parametrize("vocab", [131, 4096, 200064])
 def test_picking_tokens(vocab):
     rng = np.random.default_rng(10)
